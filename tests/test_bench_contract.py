@@ -20,11 +20,45 @@ def test_more_than_one_gpu_is_refused_with_one_line_and_exit_code_2():
     assert len(result.stdout.strip().splitlines()) == 1 and "one GPU" in result.stdout
 
 
-def test_the_reference_arm_says_why_it_is_unavailable():
+REFERENCE_KEYS = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                  "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks", "roofline", "points", "impl"}
+
+
+def test_the_reference_arm_prints_one_line_either_way():
+    """Without a GPU the arm cannot time anything: it says so in one line and exits 0."""
     result = run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
     assert result.returncode == 0
     line = json.loads(result.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and "hatchling" in line["unavailable"] and "\n" not in line["unavailable"]
+    assert line["impl"] == "reference"
+    if "unavailable" in line:
+        assert line["unavailable"] and "\n" not in line["unavailable"]
+    else:
+        assert REFERENCE_KEYS <= set(line)
+
+
+@pytest.mark.skipif(not (ROOT / "baseline" / "_ref" / "turboserve").is_dir(), reason="no reference under baseline/_ref")
+def test_the_reference_arm_runs_the_reference_and_nothing_of_this_engine():
+    """A tiny shape on the CPU through the arm's own code: the line has the contract's keys, the
+    config record is flat, and the process never imported this repository's package."""
+    script = (
+        "import sys, json; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "import bench, reference_arm as arm\n"
+        "raw = dict(bench.QWEN2_7B, num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,\n"
+        "           head_dim=16, intermediate_size=160, vocab_size=512)\n"
+        "class NoClocks(bench.ClockSampler):\n"
+        "    def start(self): pass\n"
+        "line = arm.run(raw, 'tiny', 2, 2, 256, 16, 3, 1, False, NoClocks(), bench.load_peaks(), bench.prefill_flops,\n"
+        "               device='cpu', prefill_tokens=64)\n"
+        "line['own_package_loaded'] = any(name.split('.')[0] == 'turboserve_b200' for name in sys.modules)\n"
+        "print(json.dumps(line))\n" % (str(ROOT), str(ROOT / "baseline")))
+    result = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr[-2000:]
+    line = json.loads(result.stdout.strip().splitlines()[-1])
+    assert REFERENCE_KEYS <= set(line) and line["impl"] == "reference" and not line["own_package_loaded"]
+    assert line["value"] > 0 and line["e2e"]["value"] == line["value"]
+    assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] == 16
+    assert set(line["points"]) == {"decode_b1", "decode_b64"} and line["prefill"]["tokens"] == 64
+    assert len(line["config"]) <= 20 and all(not isinstance(v, (dict, list)) for v in line["config"].values())
 
 
 def test_the_config_record_is_flat_and_short():
