@@ -70,12 +70,12 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return weight * (x * torch.rsqrt(variance + eps))
 
 
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, factor: float, dtype) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, factor: float, dtype) -> tuple[torch.Tensor, torch.Tensor]:  # noqa: E501
     """inv_freq = 1/theta^(2i/d); angles = (pos / factor) x inv_freq; emb = cat(f, f)  (model/layers.py:258-288)."""
     # The angles are float32 products, as in the reference's float32 tables; cos and sin of
     # those angles are then taken in the working precision.
     exponent = torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim
-    inv_freq = 1.0 / (theta ** exponent)
+    inv_freq = (1.0 / (theta ** exponent)).to(positions.device)
     freqs = torch.outer(positions.to(torch.float32) / factor, inv_freq)
     emb = torch.cat((freqs, freqs), dim=-1).to(dtype)
     return emb.cos(), emb.sin()
@@ -105,8 +105,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int | N
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("ihd,jhd->hij", q, k) * (d ** -0.5)
-    i = torch.arange(t)[:, None]
-    j = torch.arange(t)[None, :]
+    i = torch.arange(t, device=q.device)[:, None]
+    j = torch.arange(t, device=q.device)[None, :]
     visible = j <= i
     if window is not None:
         visible = visible & (j > i - window)
@@ -149,18 +149,32 @@ def decoder_layer(h: torch.Tensor, w: dict[str, torch.Tensor], prefix: str, dims
                    w[prefix + "mlp.down_proj.weight"], dims["act"])
 
 
-def forward_logits(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=torch.float64) -> torch.Tensor:
-    """Logits at every position of one whole sequence: [T, vocab]  (model/model.py:105-108,237-244)."""
+class _Upcast:
+    """Weights by name, upcast (and moved) one at a time when they are asked for."""
+
+    def __init__(self, weights, dtype, device) -> None:
+        self.weights, self.dtype, self.device = weights, dtype, device
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.weights[name].to(device=self.device, dtype=self.dtype)
+
+
+def forward_logits(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=torch.float64, device="cpu") -> torch.Tensor:
+    """Logits at every position of one whole sequence: [T, vocab]  (model/model.py:105-108,237-244).
+
+    ``device`` only says where the same torch calls run (a model of real widths and depth takes
+    minutes in float64 on a CPU); the result comes back on the CPU.
+    """
     dims = derived(config)
-    w = {name: value.to(dtype) for name, value in weights.items()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(ids.numel())
+    w = _Upcast(weights, dtype, device)
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(ids.numel(), device=device)
     h = embed(w["model.embed_tokens.weight"], ids)
     for layer in range(dims["L"]):
         h = decoder_layer(h, w, f"model.layers.{layer}.", dims, positions, layer_window(config, layer))
     h = rms_norm(h, w["model.norm.weight"], dims["eps"])
     head = w["model.embed_tokens.weight"] if dims["tie"] else w["lm_head.weight"]
-    return h @ head.T
+    return (h @ head.T).cpu()
 
 
 def greedy_generate(config: dict, weights: dict[str, torch.Tensor], prompt, num_tokens: int, dtype=torch.float64) -> list[int]:

@@ -134,6 +134,44 @@ def test_temperature_sampling_matches_the_plain_sampler(model_folders, name):
             assert abs(out.logprobs[i] - logprob) < 1e-4
 
 
+def test_bfloat16_sampled_rows_match_the_plain_sampler_on_the_engines_own_logits(model_folders):
+    """Temperature, top-k, top-p and a penalty in bfloat16, graphs and steps launched ahead included:
+    every sampled id is what the plain sampler draws from the very row of logits the engine's
+    sampler was given (exact ids), so a fault of the sampler cannot hide behind bfloat16 rounding."""
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+    from turboserve_b200.sampling.sampler import Sampler
+
+    class Recording(Sampler):
+        def __init__(self, device):
+            super().__init__(device)
+            self.seen = []
+
+        def sample_device(self, logits, rows, out=None):
+            tokens, logprobs = super().sample_device(logits, rows, out)
+            self.seen.append((logits[: len(rows)].clone(), [(r.params, r.seed, r.counter, list(r.history)) for r in rows], tokens.clone()))
+            return tokens, logprobs
+
+    config, _ = P.read_model_folder(model_folders["D"])
+    prompts = prompts_for(config, [9, 31, 60, 4], seed=12)
+    options = [dict(temperature=0.7, seed=11), dict(temperature=1.2, top_k=20, top_p=0.9, seed=5),
+               dict(temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3), dict(temperature=1.0, top_p=0.95)]
+    sampler = Recording("cuda")
+    engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="bfloat16", seed=3, scheduler=SchedulerConfig(
+        max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)), sampler=sampler)
+    with engine:
+        outputs = engine.generate(prompts, [SamplingParams(max_tokens=14, ignore_eos=True, **o) for o in options])
+        assert engine.stats()["num_overlapped_steps"] > 0 and engine.runner.num_graph_replays > 0
+    assert all(o.output_tokens == 14 for o in outputs)
+    checked = 0
+    for logits, rows, tokens in sampler.seen:
+        for row, (params, seed, counter, history), token in zip(logits.cpu(), rows, tokens.tolist()):
+            expect, _ = P.sample_token(row, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
+                                       repetition_penalty=params.repetition_penalty, history=history, seed=seed, counter=counter)
+            assert token == expect, (counter, token, expect)
+            checked += 1
+    assert checked == 4 * 14
+
+
 def test_long_decoding_through_many_pages_and_a_window(model_folders):
     from turboserve_b200 import SamplingParams
 
@@ -145,6 +183,35 @@ def test_long_decoding_through_many_pages_and_a_window(model_folders):
             assert engine.stats()["num_window_releases"] > 10
         assert out.output_tokens == 300
         check_greedy_path(config, weights, prompt, out.token_ids, dtype)
+
+
+def test_a_window_group_with_exactly_the_pages_of_admission_under_a_large_budget(model_folders):
+    """A token budget (251) far above the window (32): the windowed layers' pool has exactly the 37
+    pages that admission asks for, all in use during the third portion of a 760-token prompt, whose
+    first query reads from the last slot of a page. The tokens are the plain implementation's."""
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+    from turboserve_b200.engine.runner import ModelRunner, load_model, make_groups
+
+    config, weights = P.read_model_folder(model_folders["B"])
+    prompt = prompts_for(config, [760], seed=13)[0]
+    model = load_model(model_folders["B"], torch.float32)
+    groups = make_groups(model.cache_plan(), 8, [100, 37])
+    assert [g.window for g in groups] == [None, 32]
+    runner = ModelRunner(model, groups, 2)
+    engine_config = EngineConfig(model="(injected)", dtype="float32", scheduler=SchedulerConfig(
+        max_num_seqs=2, max_num_batched_tokens=251, block_size=8))
+    with LLMEngine(engine_config, runner=runner) as engine:
+        seq = engine.add_request("long", prompt, SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+        least_free = 37
+        while engine.has_unfinished():
+            engine.step()
+            least_free = min(least_free, engine.cache.free_pages()[1])
+        assert least_free == 0 and engine.stats()["num_preemptions"] == 0
+    check_greedy_path(config, weights, prompt, seq.output_token_ids, "float32")
+    smaller = ModelRunner(model, make_groups(model.cache_plan(), 8, [100, 36]), 2)
+    with LLMEngine(engine_config, runner=smaller) as engine:
+        with pytest.raises(ValueError, match="more than the cache can ever hold"):
+            engine.add_request("long", prompt, SamplingParams(max_tokens=8))
 
 
 def test_requests_step_by_step_abort_stop_and_stats(model_folders):
@@ -211,9 +278,21 @@ def test_overlapped_decode_changes_no_token(model_folders, dtype):
     assert run(True, seeded)[0] == run(False, seeded)[0]
 
 
-def test_the_engine_refuses_to_run_without_a_gpu_path():
+def test_the_engine_refuses_to_run_without_its_extension(model_folders, tmp_path, monkeypatch):
+    """No compiler and no built library: building an engine and running a step raises the build
+    error; no torch path takes over and returns tokens."""
     import turboserve_b200.ops.build as build
+    from turboserve_b200 import SamplingParams
 
-    assert build.find_nvcc()
-    with pytest.raises(build.ExtensionBuildError):
-        build.library_path("no_such_library") if "no_such_library" in build.LIBRARIES else (_ for _ in ()).throw(build.ExtensionBuildError("x"))
+    def no_compiler():
+        raise build.ExtensionBuildError("nvcc was not found (test)")
+
+    empty = tmp_path / "empty_build_dir"
+    empty.mkdir()
+    monkeypatch.setenv("TURBOSERVE_B200_BUILD_DIR", str(empty))
+    monkeypatch.setattr(build, "find_nvcc", no_compiler)
+    monkeypatch.setattr(build, "_loaded", {})
+    with pytest.raises(build.ExtensionBuildError, match="nvcc was not found"):
+        with engine_for(model_folders["A"], "bfloat16") as engine:
+            engine.generate([[1, 2, 3]], SamplingParams(max_tokens=2, temperature=0.0))
+    assert not list(empty.iterdir())

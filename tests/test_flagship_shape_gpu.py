@@ -9,7 +9,7 @@ import torch
 
 import plain_qwen2 as P
 import traces
-from tolerances import FP32_ATOL, check_logits
+from tolerances import FP32_ATOL, FP32_ATOL_REAL_WIDTHS, check_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -53,9 +53,11 @@ def test_one_layer_of_the_flagship_shape(flagship, dtype):
         for rid in requests:
             if dtype == "float32":
                 # the bound of the tiny models, or four times what a plain float32 evaluation loses
-                # at these widths, whichever is larger (the engine's sums run in another order)
+                # at these widths, whichever is larger (the engine's sums run in another order),
+                # and never more than the constant fixed beforehand for these widths
                 worst = (got[rid].double() - ref[rid]).abs().max().item()
-                bound = max(FP32_ATOL, 4.0 * plain32)
+                bound = min(max(FP32_ATOL, 4.0 * plain32), FP32_ATOL_REAL_WIDTHS)
+                print(f"one layer, {builder.__name__} {rid}: engine {worst:.3e}, plain float32 {plain32:.3e}, bound {bound:.3e}")
                 assert torch.isfinite(got[rid]).all() and worst <= bound, (builder.__name__, rid, worst, bound, plain32)
             else:
                 check_logits(got[rid], ref[rid], dtype, f"flagship layer {dtype} {builder.__name__} {rid}")

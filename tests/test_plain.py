@@ -13,7 +13,7 @@ from conftest import TINY_B
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-@pytest.mark.parametrize("name", ["gqa_tied", "mqa_untied"])
+@pytest.mark.parametrize("name", ["gqa_tied", "mqa_untied", "windowless_b"])
 def test_plain_equals_the_reference_model_code(name):
     """Logits stored by tests/golden/make_reference_golden.py from the reference's own CausalLM."""
     data = np.load(GOLDEN / f"reference_qwen2_{name}.npz")
@@ -24,6 +24,27 @@ def test_plain_equals_the_reference_model_code(name):
     assert ours.shape == theirs.shape
     # the reference computed in float32: its own rounding is what is left
     assert (ours - theirs).abs().max().item() < 5e-6
+
+
+def test_a_window_that_cannot_bind_changes_nothing_the_reference_computes():
+    """The second tiny configuration's sizes, run by the reference with the window off (it rejects
+    one): the plain implementation with the window ON equals it on a prompt shorter than the
+    window, and differs from it (so the window is really on) on the longer prompt."""
+    data = np.load(GOLDEN / "reference_qwen2_windowless_b.npz")
+    config = json.loads(bytes(data["config_json"]).decode())
+    for key in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim", "intermediate_size", "vocab_size",
+                "num_hidden_layers", "rope_theta", "rms_norm_eps", "sliding_window", "max_window_layers"):
+        assert config[key] == TINY_B[key], key
+    weights = {key[2:]: torch.from_numpy(data[key]) for key in data.files if key.startswith("w:")}
+    windowed = dict(config, use_sliding_window=True)
+    assert [P.layer_window(windowed, i) for i in range(3)] == [None, 32, 32]
+    short = P.forward_logits(windowed, weights, data["short_token_ids"].tolist())
+    assert len(data["short_token_ids"]) == 29
+    assert (short - torch.from_numpy(data["short_logits"]).double()).abs().max().item() < 5e-6
+    long_on = P.forward_logits(windowed, weights, data["token_ids"].tolist())
+    theirs = torch.from_numpy(data["logits"]).double()
+    assert (long_on[:32] - theirs[:32]).abs().max().item() < 5e-6  # the first 32 positions see everything either way
+    assert (long_on[32:] - theirs[32:]).abs().max().item() > 1e-3  # from position 32 on the window hides keys
 
 
 def test_attention_is_causal_grouped_and_windowed():

@@ -266,3 +266,41 @@ def test_no_plan_ahead_without_pages_or_for_a_prompt_that_is_cut():
     plan = s.schedule(now=0.0)  # a portion of the prompt: it does not sample
     assert not plan.scheduled[0].samples and s.continue_decode(plan) is None
     assert s.continue_decode(SchedulerOutput()) is None
+
+
+def test_a_windowed_group_with_exactly_the_pages_admission_asks_for_runs_and_one_fewer_is_refused():
+    """A token budget far above the window: a portion needs the window before it plus itself.
+
+    Window 32, pages of 8, portions of 251 tokens: the third portion starts at position 502, reads
+    from position 471 (the last slot of page 58) and writes up to 752 (page 94): 37 pages at once,
+    which is what ``pages_to_admit`` gives (36 for the 283 positions, one for the ragged start).
+    With 37 pages the request runs to its end; with 36 it is refused when it is added; and a
+    manager that is driven past that check does run out at that very portion.
+    """
+    from turboserve_b200.cache.manager import OutOfPagesError
+
+    def make_windowed(pages):
+        groups = [GroupSpec("full", None, 200, 8), GroupSpec("w", 32, pages, 8)]
+        config = SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=251, block_size=8)
+        return Scheduler(config, CacheManager(groups, 2))
+
+    s = make_windowed(37)
+    assert s.cache.pages_to_admit(760, 251) == [95, 37]
+    seq = s.add_request("a", list(range(760)), SamplingParams(max_tokens=6))
+    least_free = 37
+    portions = []
+    while s.has_unfinished():
+        plan = run_step(s)
+        portions += [(i.start, i.num_new_tokens) for i in plan.scheduled]
+        least_free = min(least_free, s.cache.free_pages()[1])
+        assert not plan.preempted and not plan.dropped
+    assert portions[:4] == [(0, 251), (251, 251), (502, 251), (753, 7)] and seq.num_output_tokens == 6
+    assert least_free == 0  # every page of the group was in use at the third portion
+    with pytest.raises(ValueError, match="more than the cache can ever hold"):
+        make_windowed(36).add_request("a", list(range(760)), SamplingParams(max_tokens=6))
+    manager = CacheManager([GroupSpec("w", 32, 36, 8)], 1)
+    manager.admit("a")
+    manager.grow("a", 251)
+    manager.grow("a", 251)
+    with pytest.raises(OutOfPagesError):
+        manager.grow("a", 251)

@@ -132,3 +132,42 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     finally:
         unregister_architecture("ToyStateForCausalLM")
         MIXERS.unregister("toy_decay")
+
+
+def test_toy_mixer_with_state_through_the_engine_with_preemption_and_a_small_budget(tmp_path):
+    """The same toy model through ``LLMEngine``: a token budget that cuts its prompts, a pool so
+    small that requests are preempted and computed again, steps launched ahead. The state must
+    be carried across portions, reset at admission and again after a preemption: every token is
+    the plain recurrence's argmax."""
+    from safetensors.torch import load_file
+
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+    from turboserve_b200.config import unregister_architecture
+    from turboserve_b200.parts import MIXERS
+    from turboserve_b200.weights import write_random_model
+
+    ToyConfig = register_toy()
+    try:
+        config = ToyConfig(hidden_size=40, vocab_size=90, decay=0.8, intermediate_size=56)
+        folder = write_random_model(config, 3, tmp_path / "toy", torch.float32)
+        weights = load_file(str(folder / "model.safetensors"))
+        prompts = list(traces.make_requests(90, [30, 9, 45, 17, 26, 38], seed=6).values())
+        engine = LLMEngine(EngineConfig(model=str(folder), dtype="float32", overlap_decode=True, scheduler=SchedulerConfig(
+            max_num_seqs=4, max_num_batched_tokens=12, block_size=4, num_blocks=16)))
+        with engine:
+            assert not engine.model.graph_safe  # the toy mixer steps on the host: never captured
+            outputs = engine.generate(prompts, SamplingParams(max_tokens=30, temperature=0.0, ignore_eos=True))
+            stats = engine.stats()
+            engine.scheduler.check_invariants()
+            assert engine.cache.slots.num_free == engine.cache.slots.num_slots
+        assert stats["num_preemptions"] > 0 and stats["num_overlapped_steps"] > 0, stats
+        for prompt, out in zip(prompts, outputs):
+            assert out.output_tokens == 30
+            logits = plain_toy(config, weights, prompt + out.token_ids)
+            for i, token in enumerate(out.token_ids):
+                row = logits[len(prompt) + i - 1]
+                best = int(row.argmax())
+                assert token == best or row[best] - row[token] <= 1e-5, (i, token, best)
+    finally:
+        unregister_architecture("ToyStateForCausalLM")
+        MIXERS.unregister("toy_decay")

@@ -93,12 +93,15 @@ def register_toys():
     return ToyConfig
 
 
-def plain_attention(x, w, p, pos, inv_freq):
-    """Causal attention, 3 query heads on one kv head of 16 dims, pairs (i, i + len/2... ) rotated by pos * inv_freq[i]."""
+def plain_attention(x, w, p, pos, inv_freq, added=None):
+    """Causal attention, 3 query heads on one kv head of 16 dims, pairs (i, i + len/2... ) rotated by pos * inv_freq[i];
+    ``added`` ([tokens, 16]) is added to every query and key head instead."""
     nh, d = 3, 16
     q = (x @ w[p + "q_proj.weight"].T).view(-1, nh, d)
     k = (x @ w[p + "k_proj.weight"].T).view(-1, 1, d)
     v = (x @ w[p + "v_proj.weight"].T).view(-1, 1, d)
+    if added is not None:
+        q, k = q + added[:, None, :], k + added[:, None, :]
     if inv_freq is not None:
         half = len(inv_freq)
         angle = pos.double()[:, None] * inv_freq.double()[None, :]
@@ -170,3 +173,103 @@ def test_toy_feed_forward_with_routing_and_another_position_encoding(tmp_path):
         unregister_architecture("ToyPartsForCausalLM")
         FEED_FORWARDS.unregister("toy_routed")
         POSITIONS.unregister("toy_listed")
+
+
+WAVE_RATES = tuple(0.37 * 0.61 ** j for j in range(16))
+WAVE_AMPLITUDE = 0.25
+
+
+def waves(positions):
+    """[tokens, 16] float64: what the toy encoding below adds to every query and key head."""
+    return WAVE_AMPLITUDE * torch.sin(positions.double()[:, None] * torch.tensor(WAVE_RATES, dtype=torch.float64, device=positions.device)[None, :])
+
+
+def test_toy_position_encoding_that_is_not_a_rotation(tmp_path):
+    """A position encoding that adds a wave of the position to queries and keys: no pair is
+    rotated, no frequency table is handed to a kernel. It overrides ``PositionEncoding.apply`` and
+    is registered here; the attention part and its kernels are used as they are."""
+    from dataclasses import dataclass
+
+    from safetensors.torch import load_file
+
+    from turboserve_b200.config import LayerSpec, ModelSpec, PartSpec, register_architecture, unregister_architecture
+    from turboserve_b200.models import DecoderModel
+    from turboserve_b200.parts import POSITIONS, PositionEncoding, register_position
+    from turboserve_b200.replay import Replayer
+    from turboserve_b200.weights import write_random_model
+
+    calls = []
+
+    class AddedWaves(PositionEncoding):
+        def __init__(self, spec, device):
+            self.heads_seen = None
+
+        def apply(self, qkv, bias, num_heads, num_kv_heads, head_dim, ctx, cache, write):
+            n = ctx.batch.num_tokens
+            wave = waves(ctx.batch.positions[:n]).to(qkv.dtype)
+            rotated_heads = num_heads + num_kv_heads  # queries and keys, not values
+            qkv[:n, : rotated_heads * head_dim].view(n, rotated_heads, head_dim).add_(wave[:, None, :])
+            calls.append((num_heads, num_kv_heads, head_dim, bool(write)))
+            self.append(qkv, bias, num_heads, num_kv_heads, head_dim, ctx, cache, write)
+
+    register_position("toy_waves", AddedWaves)
+
+    @dataclass(frozen=True)
+    class WaveConfig:
+        hidden_size: int
+        vocab_size: int
+        architecture: str = "ToyWavesForCausalLM"
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["hidden_size"], data["vocab_size"])
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], hidden_size=self.hidden_size, vocab_size=self.vocab_size)
+
+        def to_model_spec(self):
+            norm = PartSpec("rms_norm", {"eps": 1e-5})
+            attn = PartSpec("attention", dict(num_heads=3, num_kv_heads=1, head_dim=16, qkv_bias=False, window=None))
+            dense = PartSpec("gated_mlp", {"intermediate_size": 48})
+            layers = (LayerSpec(attn, dense, norm, norm, PartSpec("toy_waves", {})),
+                      LayerSpec(attn, dense, norm, norm, PartSpec("rotary", dict(rotary_dim=16, theta=1e4))))
+            return ModelSpec(self.architecture, self.hidden_size, self.vocab_size, layers, ModelSpec.sequential(2), norm)
+
+    register_architecture("ToyWavesForCausalLM", WaveConfig,
+                          lambda config, dtype, device: DecoderModel(config.to_model_spec(), dtype, device))
+
+    def plain(weights, ids, with_wave=True):
+        w = {k: v.double() for k, v in weights.items()}
+        h = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        pos = torch.arange(len(ids))
+        rotary = 1.0 / (1e4 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+        for layer in range(2):
+            p = f"model.layers.{layer}."
+            x = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+            if layer == 0:
+                h = h + plain_attention(x, w, p + "self_attn.", pos, None, added=waves(pos) if with_wave else None)
+            else:
+                h = h + plain_attention(x, w, p + "self_attn.", pos, rotary)
+            x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+            h = h + P.mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], "silu")
+        return P.rms_norm(h, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T
+
+    try:
+        config = WaveConfig(hidden_size=40, vocab_size=70)
+        folder = write_random_model(config, 8, tmp_path / "waves", torch.float32)
+        weights = load_file(str(folder / "model.safetensors"))
+        requests = traces.make_requests(70, [33, 8, 47, 21], seed=14)
+        ref = {rid: plain(weights, ids) for rid, ids in requests.items()}
+        # the wave matters: without it the logits are somewhere else
+        assert all((ref[rid] - plain(weights, ids, with_wave=False)).abs().max() > 1e-3 for rid, ids in requests.items())
+        for builder, kwargs in ((traces.whole, {}), (traces.changing_portions, {"sizes": (5, 2, 11, 1)}), (traces.mixed, {"seed": 3, "max_live": 3})):
+            steps, max_tokens = builder(requests, **kwargs)
+            replayer = Replayer(folder, "float32", max_tokens)
+            assert replayer.model.graph_safe  # nothing in it steps on the host
+            got = traces.collect(requests, steps, traces.replay(replayer, steps))
+            for rid in requests:
+                assert torch.allclose(got[rid].double(), ref[rid], atol=3e-5), (builder.__name__, rid, (got[rid].double() - ref[rid]).abs().max())
+        assert calls and set(calls) == {(3, 1, 16, True)}
+    finally:
+        unregister_architecture("ToyWavesForCausalLM")
+        POSITIONS.unregister("toy_waves")

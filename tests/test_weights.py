@@ -121,3 +121,59 @@ def test_sharded_checkpoint_and_missing_shard(tmp_path):
     (folder / "model.safetensors.index.json").write_text(json.dumps({"nothing": 1}))
     with pytest.raises(WeightLoadError, match="weight_map"):
         load_weights(model, folder)
+
+
+def test_exporter_prefixes_are_rewritten_before_names_are_compared(tmp_path):
+    """``transformer.`` / ``language_model.model.`` / ``language_model.lm_head.`` / ``model.decoder.`` in
+    front of the decoder stack load as ``model.`` / ``lm_head.``
+    (``src/turboserve/engine/model/weights.py:56-61,181-196``); a name left over is still reported."""
+    config, model = build(TINY_B)
+    folder = write_random_model(config, 1, tmp_path / "m", torch.float32)
+    plain = {name: tensor.clone() for name, tensor in load_file(str(folder / "model.safetensors")).items()}  # the file is rewritten below
+    for old_model, old_head in (("transformer.", "lm_head."), ("language_model.model.", "language_model.lm_head."),
+                                ("model.decoder.", "lm_head.")):
+        renamed = {}
+        for name, tensor in plain.items():
+            if name.startswith("model."):
+                renamed[old_model + name[len("model."):]] = tensor
+            else:
+                renamed[old_head + name[len("lm_head."):]] = tensor
+        assert "model.embed_tokens.weight" not in renamed
+        save_file(renamed, str(folder / "model.safetensors"))
+        _, fresh = build(TINY_B)
+        load_weights(fresh, folder)
+        assert torch.equal(fresh.head, plain["lm_head.weight"]) and torch.equal(fresh.embedding, plain["model.embed_tokens.weight"])
+        assert torch.equal(fresh.blocks[2].feed_forward.down, plain["model.layers.2.mlp.down_proj.weight"])
+    renamed["transformer.extra.weight"] = torch.zeros(2)
+    save_file(renamed, str(folder / "model.safetensors"))
+    with pytest.raises(WeightLoadError, match=r"unexpected tensors \(1\): model.extra.weight"):
+        load_weights(build(TINY_B)[1], folder)
+
+
+def test_parts_are_bound_one_at_a_time(tmp_path):
+    """Loading fetches a part's tensors, binds them and lets them go before the next part's are
+    read: at no time are the unfused tensors of more than one part alive."""
+    import gc
+    import weakref
+
+    config, model = build(TINY_B)
+    folder = write_random_model(config, 1, tmp_path / "m", torch.float32)
+    alive, most = [], [0]
+    bind_stream = model.bind_stream
+
+    def watching(fetch):
+        def watched(param):
+            gc.collect()
+            matrices = [ref for ref in alive if ref() is not None]
+            most[0] = max(most[0], len(matrices))
+            value = fetch(param)
+            if any(f".{n}_proj.weight" in param.name for n in "qkv") or "gate_proj" in param.name or "up_proj" in param.name:
+                alive.append(weakref.ref(value))  # tensors that bind() fuses into new ones
+            return value
+
+        bind_stream(watched)
+
+    model.bind_stream = watching
+    load_weights(model, folder)
+    # q, k and v of one attention part, or gate and up of one feed-forward; never two parts' worth
+    assert 0 < most[0] <= 3

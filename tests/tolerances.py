@@ -8,14 +8,21 @@ bfloat16: weights are identical (stored in bfloat16), activations are rounded to
 between kernels (8 bits of mantissa, relative step 2^-8 = 0.0039) while statistics, softmax,
 rotation and the residual stream are fp32. The bound on a logit is 0.02 x max(1, largest
 |logit| of the request), and 0.004 on the mean absolute difference.
+
+float32 at the widths of the named models (inner sizes of 3,584 to 18,944 where the tiny models
+have 64 to 576, eight and more layers): rounding grows with the square root of the inner size,
+about eight times here, and with depth; the bound is 1e-4 on logits of the same magnitude,
+twenty times the tiny models' bound. The tests print what they see beside it, and what a
+float32 evaluation of the plain implementation itself loses.
 """
 
 FP32_ATOL = 5e-6
+FP32_ATOL_REAL_WIDTHS = 1e-4
 BF16_REL_MAX = 0.02
 BF16_MEAN = 0.004
 
 
-def check_logits(ours, ref, dtype: str, what: str = "") -> None:
+def check_logits(ours, ref, dtype: str, what: str = "", fp32_atol: float = FP32_ATOL) -> None:
     import torch
 
     assert ours.shape == ref.shape, f"{what}: shape {tuple(ours.shape)} vs {tuple(ref.shape)}"
@@ -24,7 +31,7 @@ def check_logits(ours, ref, dtype: str, what: str = "") -> None:
     if dtype == "float32":
         worst = diff.max().item()
         where = divmod(int(diff.argmax()), diff.shape[1])
-        assert worst <= FP32_ATOL, f"{what}: max |diff| {worst:.3e} at position {where[0]}, token {where[1]}"
+        assert worst <= fp32_atol, f"{what}: max |diff| {worst:.3e} at position {where[0]}, token {where[1]}"
     else:
         scale = max(1.0, ref.abs().max().item())
         worst = diff.max().item() / scale

@@ -130,7 +130,6 @@ def kv_size_command(
     torch_dtype = resolve_dtype(dtype)
     built = lookup(config.architecture).build_model(config, torch_dtype, "cpu")
     itemsize = torch.empty((), dtype=torch_dtype).element_size()
-    widest = max([built.hidden_size] + [getattr(b.feed_forward, "intermediate_size", 0) for b in built.blocks])
     memory_info = None
     if total_memory_gib is not None:
         total = int(total_memory_gib * (1 << 30))
@@ -138,7 +137,7 @@ def kv_size_command(
         memory_info = (total - weights, total)
     sizing = size_kv_cache(
         built.cache_plan(), SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, block_size=block_size),
-        itemsize, hidden=built.hidden_size, widest=widest, vocab=built.vocab_size,
+        itemsize, scratch_per_token=built.scratch_bytes_per_token(itemsize), vocab=built.vocab_size,
         gpu_memory_utilization=gpu_memory_utilization, max_model_len=max_model_len, memory_info=memory_info,
     )
     typer.echo(json.dumps(sizing.to_dict(), indent=2))

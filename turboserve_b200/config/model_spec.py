@@ -78,7 +78,10 @@ class TensorNames:
     """How an architecture's checkpoint names its tensors.
 
     ``layer`` is formatted with the layer index; the four part prefixes are appended to it and
-    each part appends its own local names (``q_proj.weight`` and so on).
+    each part appends its own local names (``q_proj.weight`` and so on). ``prefix_rewrites``
+    are prefixes some exporters put in front of the decoder stack, with what the names above
+    expect in their place; the first that matches a checkpoint name is applied, once
+    (``src/turboserve/engine/model/weights.py:56-61,181-196``).
     """
 
     embedding: str = "model.embed_tokens.weight"
@@ -89,6 +92,12 @@ class TensorNames:
     feed_forward: str = "mlp."
     mixer_norm: str = "input_layernorm."
     feed_forward_norm: str = "post_attention_layernorm."
+    prefix_rewrites: tuple[tuple[str, str], ...] = (
+        ("transformer.", "model."),
+        ("language_model.model.", "model."),
+        ("language_model.lm_head.", "lm_head."),
+        ("model.decoder.", "model."),
+    )
 
 
 @dataclass(frozen=True)

@@ -55,11 +55,10 @@ class LLMEngine:
             if model is None:
                 model = load_model(config.model, dtype, device)
             plan = model.cache_plan()
-            widest = max([model.hidden_size] + [getattr(b.feed_forward, "intermediate_size", 0) for b in model.blocks]
-                         + [getattr(b.mixer, "qkv_width", 0) for b in model.blocks])
+            itemsize = torch.empty((), dtype=dtype).element_size()
             self.sizing = size_kv_cache(
-                plan, config.scheduler, torch.empty((), dtype=dtype).element_size(), hidden=model.hidden_size,
-                widest=widest, vocab=model.vocab_size, gpu_memory_utilization=config.gpu_memory_utilization,
+                plan, config.scheduler, itemsize, scratch_per_token=model.scratch_bytes_per_token(itemsize),
+                vocab=model.vocab_size, gpu_memory_utilization=config.gpu_memory_utilization,
                 max_model_len=config.max_model_len, device=device,
             )
             groups = make_groups(plan, config.scheduler.block_size, self.sizing.num_blocks)

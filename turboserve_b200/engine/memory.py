@@ -34,14 +34,22 @@ class KVCacheSizing:
         return asdict(self)
 
 
-def activation_headroom_bytes(hidden: int, widest: int, vocab: int, itemsize: int, scheduler: SchedulerConfig) -> int:
-    """Scratch the step needs at its largest batch: activations, the fp32 residual and logits."""
-    tokens = scheduler.max_num_batched_tokens
-    per_token = 4 * hidden + itemsize * (3 * hidden + 3 * widest)
-    return tokens * per_token + 2 * scheduler.max_num_seqs * vocab * 4
+def activation_headroom_bytes(scratch_per_token: int, vocab: int, scheduler: SchedulerConfig) -> int:
+    """Scratch the step needs at its largest batch: what the model's parts declare per token
+    (``DecoderModel.scratch_bytes_per_token``), and fp32 logits for every request, twice."""
+    return scheduler.max_num_batched_tokens * scratch_per_token + 2 * scheduler.max_num_seqs * vocab * 4
 
 
-def size_kv_cache(plan: CachePlan, scheduler: SchedulerConfig, itemsize: int, *, hidden: int, widest: int, vocab: int,
+def device_memory_info(device: torch.device | None = None) -> tuple[int, int]:
+    """``(free, total)`` bytes as the sizing wants them: memory that torch's allocator holds but has
+    handed to nobody (freed originals of fused weights, for instance) counts as free, since the
+    cache is allocated through the same allocator and gets it."""
+    free, total = torch.cuda.mem_get_info(device)
+    cached = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+    return free + max(0, cached), total
+
+
+def size_kv_cache(plan: CachePlan, scheduler: SchedulerConfig, itemsize: int, *, scratch_per_token: int, vocab: int,
                   gpu_memory_utilization: float = 0.9, max_model_len: int | None = None,
                   device: torch.device | None = None, memory_info: tuple[int, int] | None = None) -> KVCacheSizing:
     block = scheduler.block_size
@@ -56,10 +64,10 @@ def size_kv_cache(plan: CachePlan, scheduler: SchedulerConfig, itemsize: int, *,
         return KVCacheSizing(blocks, block, groups, per_page, state, blocks * per_page + state, "explicit",
                              max_tokens=blocks * block)
     if memory_info is None:
-        memory_info = torch.cuda.mem_get_info(device)
+        memory_info = device_memory_info(device)
     free, total = memory_info
     used = total - free
-    activations = activation_headroom_bytes(hidden, widest, vocab, itemsize, scheduler)
+    activations = activation_headroom_bytes(scratch_per_token, vocab, scheduler)
     budget = int(gpu_memory_utilization * total) - used - activations - state
     blocks = budget // per_page
     if blocks < 1:

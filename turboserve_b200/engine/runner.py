@@ -156,8 +156,8 @@ class ModelRunner:
         """
         if self._graph_buckets:
             return
-        if any(run.kind == "state" for run in self.plan.runs):
-            return  # a mixer with state of its own may step on the host; such models run eagerly
+        if not self.model.graph_safe:
+            return  # a part of this model may step on the host (Part.graph_safe): it runs eagerly
         self.reserve(max(max_tokens or 0, max_seqs, 1), max_seqs)
         buckets, b = [], 1
         while b < max_seqs:

@@ -17,7 +17,7 @@ from ..cache.storage import CachePlan, CacheStorage, plan_cache
 from ..config.model_spec import ModelSpec
 from ..ops import kernels
 from ..ops.linear import linear
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, ParamSpec, Part
+from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, UNDECLARED_SCRATCH_WIDTHS, ParamSpec, Part
 
 
 @dataclass(frozen=True)
@@ -82,32 +82,52 @@ class DecoderModel:
         """Names a checkpoint may hold that are not loaded (the tied head's copy)."""
         return {self.spec.names.head} if self.spec.tie_word_embeddings else set()
 
-    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        """Hand every part its tensors (already on the device, in their final dtypes)."""
-        params = self.named_params()
-        per_part: dict[int, dict[str, torch.Tensor]] = {}
-        for p in params:
-            t = tensors[p.name]
+    def bind_stream(self, fetch) -> None:
+        """Hand every part its tensors, one part at a time.
+
+        ``fetch(param)`` returns the tensor of a :class:`NamedParam` on the device in its final
+        dtype; it is called once per tensor, in the order of :meth:`named_params`. A part's
+        tensors are bound (and fused, where the part fuses them) and let go before the next
+        part's are fetched, so that loading needs room for the model plus one part.
+        """
+        current: dict[str, torch.Tensor] = {}
+        owner = -1
+
+        def flush() -> None:
+            if owner >= 0:
+                self.parts_list[owner].bind(current)
+
+        for p in self.named_params():
+            t = fetch(p)
             if tuple(t.shape) != tuple(p.spec.shape):
                 raise ValueError(f"{p.name}: shape {tuple(t.shape)} where {p.spec.shape} is declared")
+            if p.owner != owner:
+                flush()
+                current, owner = {}, p.owner
             if p.owner >= 0:
-                per_part.setdefault(p.owner, {})[p.local] = t
-        self.embedding = tensors[self.spec.names.embedding].contiguous()
-        self.head = self.embedding if self.spec.tie_word_embeddings else tensors[self.spec.names.head].contiguous()
+                current[p.local] = t
+            elif p.local == "embedding":
+                self.embedding = t.contiguous()
+            else:
+                self.head = t.contiguous()
+        flush()
+        if self.spec.tie_word_embeddings:
+            self.head = self.embedding
         for index, part in enumerate(self.parts_list):
-            part.bind(per_part.get(index, {}))
+            if not part.param_specs():
+                part.bind({})
         self.loaded = True
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Hand every part its tensors from a dict by full name (device, final dtypes)."""
+        self.bind_stream(lambda p: tensors[p.name])
 
     def init_random(self, seed: int) -> None:
         """Fill the model with random weights made on the device (large shapes, benchmarks)."""
         from ..weights.random_init import draw
 
         generator = torch.Generator(device=self.device).manual_seed(seed)
-        tensors = {}
-        for p in self.named_params():
-            value = draw(p.spec, self.spec.init_std, generator, self.device)
-            tensors[p.name] = value.to(p.spec.device_dtype(self.dtype))
-        self.bind(tensors)
+        self.bind_stream(lambda p: draw(p.spec, self.spec.init_std, generator, self.device).to(p.spec.device_dtype(self.dtype)))
 
     def num_parameters(self) -> int:
         total = 0
@@ -117,6 +137,24 @@ class DecoderModel:
                 count *= s
             total += count
         return total
+
+    # -- what the parts declare -----------------------------------------------------------------
+
+    def scratch_bytes_per_token(self, itemsize: int) -> int:
+        """Scratch a step holds per token: the fp32 residual, the normed rows, and the most that
+        any layer's mixer and feed-forward declare (buffers are shared between layers by name)."""
+        def declared(part: Part) -> int:
+            own = part.scratch_per_token()
+            return UNDECLARED_SCRATCH_WIDTHS * self.hidden_size if own is None else int(own)
+
+        mixers = max(declared(block.mixer) for block in self.blocks)
+        feed_forwards = max(declared(block.feed_forward) for block in self.blocks)
+        return 4 * self.hidden_size + itemsize * (self.hidden_size + mixers + feed_forwards)
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether every part allows its step to be captured in a CUDA graph (``Part.graph_safe``)."""
+        return all(part.graph_safe for part in self.parts_list)
 
     # -- cache ------------------------------------------------------------------------------
 

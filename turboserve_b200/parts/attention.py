@@ -19,7 +19,6 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import PartSpec
-from ..ops import kernels
 from ..ops.attention import paged_attention
 from ..ops.linear import linear
 from .base import MIXERS, POSITIONS, Mixer, PagedKVNeed, ParamSpec, register_mixer
@@ -45,8 +44,8 @@ class PagedAttention(Mixer):
         if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
             raise ValueError(f"head_dim must be a multiple of 16 between 16 and 256, got {self.head_dim}")
         self.position = POSITIONS.get(position.kind)(position, device) if position is not None else NoPosition()
-        if getattr(self.position, "rotary_dim", 0) > self.head_dim:
-            raise ValueError("rotary_dim exceeds head_dim")
+        self.position.check(self.head_dim)
+        self.graph_safe = bool(self.position.graph_safe)
         self.proj_kv_heads = 0 if self.shares_cache else self.num_kv_heads
         self.qkv_width = (self.num_heads + 2 * self.proj_kv_heads) * self.head_dim
         self.qkv: torch.Tensor | None = None
@@ -56,6 +55,9 @@ class PagedAttention(Mixer):
 
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def scratch_per_token(self) -> int:
+        return self.qkv_width + self.num_heads * self.head_dim + self.hidden_size
 
     def param_specs(self) -> list[ParamSpec]:
         h, d = self.hidden_size, self.head_dim
@@ -85,11 +87,8 @@ class PagedAttention(Mixer):
         table = batch.block_tables[cache.group]
         qkv = ctx.buffer("attn.qkv", (n, self.qkv_width))
         linear(x, self.qkv, qkv, None, n, ctx)
-        kernels.rope_cache_write(
-            qkv, self.qkv_b, batch.positions, batch.seq_of_token, table, cache.k_pages, cache.v_pages, n,
-            self.num_heads, self.proj_kv_heads, self.head_dim, self.position.inv_freq, self.position.rotary_dim,
-            self.position.factor, cache.writes and not self.shares_cache, ctx.status,
-        )
+        self.position.apply(qkv, self.qkv_b, self.num_heads, self.proj_kv_heads, self.head_dim, ctx, cache,
+                            cache.writes and not self.shares_cache)
         attended = ctx.buffer("attn.attended", (n, self.num_heads * self.head_dim))
         paged_attention(
             qkv, attended, cache.k_pages, cache.v_pages, table, batch, self.num_heads, self.num_kv_heads,

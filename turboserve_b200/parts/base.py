@@ -77,13 +77,35 @@ class StateNeed:
 
 
 class Part:
-    """Base of every part: declared tensors in, bound tensors kept."""
+    """Base of every part: declared tensors in, bound tensors kept.
+
+    ``graph_safe`` says that ``forward`` only queues work on the device from tensors whose
+    addresses and shapes stay the same from step to step: it never reads a value back, never
+    loops on the host over what a request brings, and takes its scratch from ``ctx.buffer``. Decode steps of a
+    model are replayed from CUDA graphs only if every one of its parts says so; the default
+    is the careful one, so a part written without a thought for graphs is never captured.
+    """
+
+    graph_safe = False
 
     def param_specs(self) -> list[ParamSpec]:
         return []
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         """Receive the tensors named by :meth:`param_specs` (device, final dtype)."""
+
+    def scratch_per_token(self) -> int | None:
+        """Elements of scratch, in the activation dtype, that ``forward`` holds per token of a step.
+
+        The engine leaves that much room beside the cache when it sizes the page pool. ``None``
+        (the default) means "not declared": the model then assumes
+        :data:`UNDECLARED_SCRATCH_WIDTHS` times its hidden size for the part.
+        """
+        return None
+
+
+UNDECLARED_SCRATCH_WIDTHS = 4
+"""Hidden sizes of scratch per token assumed for a part that does not declare its own."""
 
 
 class Mixer(Part):
@@ -128,7 +150,62 @@ class Norm(Part):
 
 
 class PositionEncoding:
-    """Whatever turns positions into a change of queries and keys; used by a mixer."""
+    """Whatever turns positions into a change of queries and keys; a mixer calls :meth:`apply`.
+
+    ``apply`` is the whole step between a mixer's fused q/k/v product and its attention: add
+    the bias, change queries and keys by their positions, and append keys and values to the
+    request's pages. The mixer names no constant of the encoding; it hands over the product
+    and says how it is laid out.
+
+    The default implementation is the fused kernel of ``layer_ops.cu``: bias, then a rotation of
+    the pairs ``(i, i + rotary_dim / 2)`` of every head by ``(position / factor) * inv_freq[i]``,
+    then the append. An encoding that is such a rotation only sets ``inv_freq`` (float32,
+    ``rotary_dim / 2`` values on the device), ``rotary_dim`` and ``factor``; with ``rotary_dim``
+    0 (the class's own values) nothing is rotated. Any other encoding overrides :meth:`apply`,
+    changes ``qkv`` as it likes and calls ``super().apply`` (or :meth:`append`) for the bias and
+    the append.
+    """
+
+    graph_safe = True
+    inv_freq: torch.Tensor | None = None
+    rotary_dim = 0
+    factor = 1.0
+
+    def check(self, head_dim: int) -> None:
+        """Refuse a head size the encoding cannot act on (called once, when the mixer is built)."""
+        if self.rotary_dim > head_dim:
+            raise ValueError(f"rotary_dim ({self.rotary_dim}) exceeds head_dim ({head_dim})")
+
+    def apply(self, qkv: torch.Tensor, bias: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
+              ctx: Any, cache: Any, write: bool) -> None:
+        """Encode in place and append to the cache.
+
+        ``qkv`` is ``[tokens, (num_heads + 2 * num_kv_heads) * head_dim]``: the query heads, then
+        the key heads, then the value heads of every token of the step (``num_kv_heads`` is 0
+        when the mixer reads another run's cache); ``bias`` (float32, same width) or ``None``;
+        ``ctx.batch`` gives ``positions`` and ``seq_of_token``; ``cache`` the run's pages and
+        its group, whose block table is ``ctx.batch.block_tables[cache.group]``; ``write`` says
+        whether keys and values are to be appended.
+        """
+        from ..ops import kernels
+
+        batch = ctx.batch
+        kernels.rope_cache_write(
+            qkv, bias, batch.positions, batch.seq_of_token, batch.block_tables[cache.group], cache.k_pages,
+            cache.v_pages, batch.num_tokens, num_heads, num_kv_heads, head_dim, self.inv_freq, self.rotary_dim,
+            self.factor, write, ctx.status,
+        )
+
+    def append(self, qkv: torch.Tensor, bias: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
+               ctx: Any, cache: Any, write: bool) -> None:
+        """Bias and append alone, whatever the encoding's constants are."""
+        from ..ops import kernels
+
+        batch = ctx.batch
+        kernels.rope_cache_write(
+            qkv, bias, batch.positions, batch.seq_of_token, batch.block_tables[cache.group], cache.k_pages,
+            cache.v_pages, batch.num_tokens, num_heads, num_kv_heads, head_dim, None, 0, 1.0, write, ctx.status,
+        )
 
 
 class Registry:

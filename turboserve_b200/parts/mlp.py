@@ -17,6 +17,8 @@ from .base import FeedForward, ParamSpec, register_feed_forward
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(spec["intermediate_size"])
@@ -45,6 +47,9 @@ class GatedMLP(FeedForward):
                 ParamSpec("down_proj.bias", (h,), role="bias", init="bias_normal"),
             ]
         return specs
+
+    def scratch_per_token(self) -> int:
+        return 3 * self.intermediate_size + self.hidden_size  # gate and up, their product, the output
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.gate_up, self.gate_block = interleave_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])

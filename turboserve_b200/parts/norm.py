@@ -17,6 +17,8 @@ from .base import Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
         self.eps = float(spec["eps"])
         self.hidden_size = int(hidden_size)
@@ -28,6 +30,9 @@ class RMSNorm(Norm):
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.gain = tensors["weight"]
+
+    def scratch_per_token(self) -> int:
+        return 0  # it writes into the block's buffer
 
     def forward(self, residual, delta, out, ctx):
         kernels.add_rmsnorm(residual, delta, self.gain, self.eps, out, None, ctx.batch.num_tokens)

@@ -1,5 +1,5 @@
 """Rotary position encoding (NeoX halves): the constants; the rotation itself runs fused
-with the bias add and the cache append in ``layer_ops.cu``.
+with the bias add and the cache append in ``layer_ops.cu`` (``PositionEncoding.apply``).
 
 ``inv_freq[i] = 1 / theta^(2i / rotary_dim)`` in float32, ``angle = (float32(pos) / factor) *
 inv_freq[i]``, the pair ``(i, i + rotary_dim / 2)`` is rotated by it, as
@@ -30,11 +30,7 @@ class RotaryPosition(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
-    """No position encoding: queries and keys are used as projected."""
-
-    rotary_dim = 0
-    factor = 1.0
-    inv_freq = None
+    """No position encoding: queries and keys are used as projected (bias and append only)."""
 
     def __init__(self, spec: PartSpec | None = None, device: torch.device | str | None = None) -> None:
         pass

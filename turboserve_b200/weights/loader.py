@@ -82,16 +82,25 @@ def _read_header(path: Path) -> dict[str, tuple[tuple[int, ...], str]]:
     return out
 
 
-def checkpoint_index(model_dir: str | Path) -> dict[str, tuple[Path, tuple[int, ...], str]]:
-    """Every tensor of the checkpoint: name -> (file, shape, stored dtype)."""
-    index: dict[str, tuple[Path, tuple[int, ...], str]] = {}
+def map_name(stored: str, rewrites: tuple[tuple[str, str], ...] = ()) -> str:
+    """The name the model knows a checkpoint tensor by: the first matching prefix is rewritten."""
+    for old, new in rewrites:
+        if stored.startswith(old):
+            return new + stored[len(old):]
+    return stored
+
+
+def checkpoint_index(model_dir: str | Path, rewrites: tuple[tuple[str, str], ...] = ()) -> dict[str, tuple[Path, tuple[int, ...], str, str]]:
+    """Every tensor of the checkpoint: name -> (file, shape, stored dtype, name in the file)."""
+    index: dict[str, tuple[Path, tuple[int, ...], str, str]] = {}
     for path in safetensors_files(model_dir):
-        for name, (shape, dtype) in _read_header(path).items():
-            if name.endswith(SKIPPED_SUFFIXES):
+        for stored, (shape, dtype) in _read_header(path).items():
+            if stored.endswith(SKIPPED_SUFFIXES):
                 continue
+            name = map_name(stored, rewrites)
             if name in index:
                 raise WeightLoadError(f"tensor {name} is in both {index[name][0].name} and {path.name}")
-            index[name] = (path, shape, dtype)
+            index[name] = (path, shape, dtype, stored)
     return index
 
 
@@ -121,21 +130,29 @@ def load_weights(model, model_dir: str | Path) -> dict[str, str]:
     """Check the checkpoint against ``model`` and bind its tensors; returns name -> stored dtype."""
     from safetensors import safe_open
 
-    index = checkpoint_index(model_dir)
+    index = checkpoint_index(model_dir, tuple(model.spec.names.prefix_rewrites))
     check_checkpoint(model, index)
-    by_file: dict[Path, list] = {}
-    for param in model.named_params():
-        by_file.setdefault(index[param.name][0], []).append(param)
-    tensors: dict[str, torch.Tensor] = {}
     stored: dict[str, str] = {}
-    for path, params in by_file.items():
-        with safe_open(str(path), framework="pt", device="cpu") as handle:
-            for param in params:
-                value = handle.get_tensor(param.name)
-                stored[param.name] = index[param.name][2]
-                target = param.spec.device_dtype(model.dtype)
-                if target == torch.int32 and value.dtype.is_floating_point:
-                    raise WeightLoadError(f"{param.name} is an integer table but is stored as {value.dtype}")
-                tensors[param.name] = value.to(device=model.device, dtype=target)
-    model.bind(tensors)
+    handles: dict[Path, object] = {}
+
+    def fetch(param) -> torch.Tensor:
+        path, _, dtype, name_in_file = index[param.name]
+        if path not in handles:
+            handles[path] = safe_open(str(path), framework="pt", device="cpu")
+        value = handles[path].get_tensor(name_in_file)
+        stored[param.name] = dtype
+        target = param.spec.device_dtype(model.dtype)
+        if target == torch.int32 and value.dtype.is_floating_point:
+            raise WeightLoadError(f"{param.name} is an integer table but is stored as {value.dtype}")
+        return value.to(device=model.device, dtype=target)
+
+    # part by part: a part's tensors go up, are fused by its bind() and dropped before the next
+    # part's are read, so the device never holds much more than the model itself
+    try:
+        model.bind_stream(fetch)
+    finally:
+        for handle in handles.values():
+            close = getattr(handle, "__exit__", None)
+            if close is not None:
+                close(None, None, None)
     return stored
