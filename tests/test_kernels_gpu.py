@@ -707,3 +707,29 @@ def test_linear_rule_picks_a_kernel_for_every_shape():
             out = torch.empty(m, n, dtype=dtype, device=DEV)
             linear(a.to(DEV), w.to(DEV), out, bias.to(DEV))
             assert (out.double().cpu() - ref).abs().max().item() < 0.06, (m, n, k, dtype)
+
+
+def test_a_row_of_float32_logits_does_not_depend_on_how_many_rows_are_asked_for():
+    """Up to 64 rows the head runs the tcgen05 product, beyond that the library: both hand back
+    float32 accumulators (not a rounded bfloat16 result), so the same row of activations gives
+    logits that differ by rounding of the sum only, far below a bfloat16 step, whether it is one
+    of 3 rows or of 65. A bfloat16 detour would tie hundreds of a wide vocabulary's logits."""
+    from turboserve_b200.ops.linear import linear
+
+    torch.manual_seed(5)
+    k, n = 256, 20000
+    w = (torch.randn(n, k) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    x = torch.randn(65, k).to(torch.bfloat16).to(DEV)
+    few = torch.empty(3, n, dtype=torch.float32, device=DEV)
+    many = torch.empty(65, n, dtype=torch.float32, device=DEV)
+    linear(x[:3].contiguous(), w, few)
+    linear(x, w, many)
+    ref = (x[:3].double() @ w.double().T)
+    assert (few.double() - ref).abs().max().item() < 1e-5 and (many[:3].double() - ref).abs().max().item() < 1e-5
+    # not values on the bfloat16 grid
+    assert (many[:3] != many[:3].to(torch.bfloat16).float()).float().mean().item() > 0.9
+    biased = torch.empty(65, n, dtype=torch.bfloat16, device=DEV)
+    bias = torch.randn(n, device=DEV)
+    linear(x, w, biased, bias)
+    assert torch.equal(biased[:3], (ref + bias.double()).to(torch.bfloat16)) or \
+        ((biased[:3].double() - (ref + bias.double())).abs() <= (ref + bias.double()).abs() * 2 ** -8).all()

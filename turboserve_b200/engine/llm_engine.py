@@ -163,12 +163,28 @@ class LLMEngine:
                 self._num_overlapped_steps += 1
             outputs += self._process(flight.plan, flight.result())
         except BaseException:
-            self._in_flight = None
+            self._abandon(flight)
             raise
         if self._in_flight is not None and all(seq.is_finished for seq in self._in_flight.plan.sampling_seqs()):
             self._in_flight = None  # nobody is left to take its tokens
         self._step_seconds += time.perf_counter() - started
         return outputs
+
+    def _abandon(self, flight: "_Flight") -> None:
+        """A step failed (a kernel flagged its input, a CUDA error): end its requests.
+
+        Their tokens of this step never arrived, and what the step wrote into their pages is
+        not to be trusted; the step launched ahead of it ran on the same tokens. Left alone they
+        would hold their pages with nothing left to compute and never be scheduled again, so a
+        caller that catches the error and goes on stepping would spin. They finish with
+        ``abort`` and give everything back; other requests are untouched.
+        """
+        plans = [flight.plan] + ([self._in_flight.plan] if self._in_flight is not None else [])
+        self._in_flight = None
+        for plan in plans:
+            for item in plan.scheduled:
+                if not item.seq.is_finished:
+                    self.scheduler.finish(item.seq, FinishReason.ABORT)
 
     def _plan_ahead(self, flight: "_Flight") -> SchedulerOutput | None:
         if not self.config.overlap_decode or flight.read is None:

@@ -17,8 +17,11 @@ fallback chain:
   features its last blocks run nearly alone and the library wins (5,120 features: 16.1 against
   11.8 µs for 5,120 inputs, 37.9 against 26.6 µs for 13,824), so those go to the library.
 * every other bfloat16 shape: cuBLAS through ``torch.mm``, as the reference does for every
-  product (``src/turboserve/engine/model/layers.py:142``); float32 output is a cast of its
-  bfloat16 result, as in ``src/turboserve/engine/model/model.py:243-244``.
+  product (``src/turboserve/engine/model/layers.py:142``). Where the output is float32 (the
+  output head) or a bias is to be added, the library writes its float32 accumulators and the
+  bias is added to them, as in every other path here, so a row of logits does not depend on how
+  many rows were asked for (the reference casts a bfloat16 result,
+  ``src/turboserve/engine/model/model.py:243-244``).
 
 :func:`gated_linear` is the gate/up projection with its activation: for at most
 :data:`TC_MAX_ROWS` bfloat16 rows the tcgen05 kernel applies ``act(gate) * up`` in its epilogue,
@@ -61,16 +64,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch
             skinny.gemm_skinny(x, weight, out, bias, m)
             return out
     xs, os_ = x[:m], out[:m]
-    if out.dtype == torch.bfloat16:
+    if out.dtype == torch.bfloat16 and bias is None:
         torch.mm(xs, weight.t(), out=os_)
-        if bias is not None:
-            os_.add_(bias.to(torch.bfloat16))
-    else:
-        tmp = torch.mm(xs, weight.t())
-        if bias is not None:
-            os_.copy_(tmp.float() + bias)
-        else:
-            os_.copy_(tmp)
+        return out
+    wide = torch.mm(xs, weight.t(), out_dtype=torch.float32)
+    if bias is not None:
+        wide.add_(bias)
+    os_.copy_(wide)
     return out
 
 
