@@ -733,3 +733,111 @@ def test_a_row_of_float32_logits_does_not_depend_on_how_many_rows_are_asked_for(
     linear(x, w, biased, bias)
     assert torch.equal(biased[:3], (ref + bias.double()).to(torch.bfloat16)) or \
         ((biased[:3].double() - (ref + bias.double())).abs() <= (ref + bias.double()).abs() * 2 ** -8).all()
+
+
+@pytest.mark.parametrize("nh, nkv, page, window, rotary_dim, with_bias", [
+    (28, 4, 16, None, 128, True), (7, 1, 16, None, 128, False), (10, 2, 8, 70, 64, True), (16, 1, 64, None, 0, True),
+    (3, 3, 4, 33, 128, True),
+])
+@pytest.mark.parametrize("splits", [1, 3, 8, 9])
+def test_decode_attention_that_encodes_and_appends_itself_equals_the_two_kernel_path(nh, nkv, page, window, rotary_dim, with_bias, splits):
+    """``flash_decode_tma_fused`` takes the raw q/k/v product: bias, rotation and the append to the cache
+    happen inside it. Same output (to a bfloat16 step of the softmax's different order) and the
+    very same bytes in the cache as the rotation kernel followed by the TMA-fed decode kernel;
+    nothing but each token's own slot of the pages is written, the product itself is not touched."""
+    from turboserve_b200.ops import attention_bf16 as fa
+    from turboserve_b200.ops import kernels
+
+    d = 128
+    contexts = [1, 37, 300, 64, 129, 1000, 65, 128]  # position 0, page edges, a token whose own tile holds no cached key (pos 64, 128)
+    k_dense, v_dense, k_pages, v_pages, table = paged_layout(contexts, page, nkv, d, torch.bfloat16, DEV, seed=41)
+    n = len(contexts) + 1  # one padding token
+    gen = torch.Generator().manual_seed(42)
+    width = (nh + 2 * nkv) * d
+    qkv = torch.randn(n, width + 8, generator=gen).to(torch.bfloat16).to(DEV)  # a row stride wider than the heads
+    bias = torch.randn(width, generator=gen).to(DEV) if with_bias else None
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / max(rotary_dim, 1)))).to(DEV) if rotary_dim else None
+    positions = torch.tensor([c - 1 for c in contexts] + [0], dtype=torch.int32, device=DEV)
+    seq_of = torch.tensor(list(range(len(contexts))) + [-1], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scratch = torch.full((max(4, fa.decode_scratch_floats(n, nh, splits, d)),), float("nan"), device=DEV)
+
+    # the two-kernel path on copies
+    qkv_a, k_a, v_a = qkv.clone(), k_pages.clone(), v_pages.clone()
+    kernels.rope_cache_write(qkv_a, bias, positions, seq_of, table, k_a, v_a, n, nh, nkv, d, inv_freq, rotary_dim, 2.0, True, status)
+    out_a = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fa.flash_decode_tma(qkv_a, out_a, k_a, v_a, table, seq_of, positions, n, nh, nkv, d, window, scale, splits, scratch, status)
+    # the fused kernel on the originals
+    qkv_b, k_b, v_b = qkv.clone(), k_pages.clone(), v_pages.clone()
+    out_b = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fusion = fa.DecodeFusion(bias, inv_freq, rotary_dim, 2.0, True)
+    fa.flash_decode_tma_fused(qkv_b, fusion, out_b, k_b, v_b, table, seq_of, positions, n, nh, nkv, d, window, scale, splits, scratch, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.equal(qkv_b, qkv)                                   # the product is read only
+    assert torch.equal(k_b, k_a) and torch.equal(v_b, v_a)           # the same bytes appended, nothing else touched
+    assert not torch.equal(k_b, k_pages)
+    live = len(contexts)
+    assert torch.isfinite(out_b[:live].float()).all() and torch.isnan(out_b[live:].float()).all()
+    assert (out_b[:live].float() - out_a[:live].float()).abs().max().item() <= 2.0 ** -6 * max(1.0, out_a[:live].float().abs().max().item())
+    # and against float64 from the appended cache: the dense keys with the token's own (rotated) key and value at the end
+    for s, ctx in enumerate(contexts):
+        rows = table[s].cpu().tolist()
+        k_all = torch.cat([k_a[rows[p // page], p % page][None] for p in range(ctx)]).float().cpu()
+        v_all = torch.cat([v_a[rows[p // page], p % page][None] for p in range(ctx)]).float().cpu()
+        q_rot = qkv_a[s, : nh * d].view(1, nh, d).float().cpu()
+        ref = attention_reference(q_rot, k_all, v_all, torch.tensor([ctx - 1]), window, scale)
+        assert (out_b[s].view(1, nh, d).double().cpu() - ref).abs().max().item() < 2e-2, s
+    # without the append (a run that only reads): the cache is left alone and the token still sees itself
+    k_c, v_c = k_pages.clone(), v_pages.clone()
+    out_c = torch.empty_like(out_b)
+    fa.flash_decode_tma_fused(qkv_b, fa.DecodeFusion(bias, inv_freq, rotary_dim, 2.0, False), out_c, k_c, v_c, table, seq_of,
+                              positions, n, nh, nkv, d, window, scale, splits, scratch, status)
+    assert torch.equal(k_c, k_pages) and torch.equal(v_c, v_pages) and torch.equal(out_c[:live], out_b[:live])
+
+
+@pytest.mark.parametrize("kind", ["registers", "registers64", "tma", "fused"])
+def test_decode_kernels_mask_and_flag_a_page_that_is_missing_inside_the_visible_keys(kind):
+    """A table entry of -1 inside a request's visible keys (a page given back too early) is never
+    read as if it held zeros: its keys get no weight, and bit 4 of the status word says so.
+    A page that is missing where no key is visible (behind a window) raises nothing."""
+    from turboserve_b200.ops import attention_bf16 as fa
+
+    nh, nkv, page = 4, 2, 16
+    d = 64 if kind == "registers64" else 128
+    ctx, lost = 200, 5  # page 5 holds keys 80 .. 95
+    k_dense, v_dense, k_pages, v_pages, table = paged_layout([ctx], page, nkv, d, torch.bfloat16, DEV, seed=51)
+    q, positions, seq_of = pack_queries([ctx], [1], nh, d, torch.bfloat16, DEV, seed=52)
+    q = q.to(DEV).view(1, nh * d)
+    scale = 1.0 / math.sqrt(d)
+    keep = torch.ones(ctx, dtype=torch.bool)
+    keep[lost * page:(lost + 1) * page] = False
+    # what the softmax over the other keys gives: positions are what matters to the mask, so drop the rows and keep causality trivial
+    ref = attention_reference(q.view(1, nh, d).float().cpu(), k_dense[0][keep], v_dense[0][keep], torch.tensor([int(keep.sum()) - 1]), None, scale)
+
+    def run(tab, window):
+        out = torch.full((1, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(max(4, fa.decode_scratch_floats(1, nh, 3, d)), device=DEV)
+        if kind.startswith("registers"):
+            fa.flash_decode(q, out, k_pages, v_pages, tab, seq_of, positions, 1, nh, nkv, d, window, scale, 3, scratch, status)
+        elif kind == "tma":
+            fa.flash_decode_tma(q, out, k_pages, v_pages, tab, seq_of, positions, 1, nh, nkv, d, window, scale, 3, scratch, status)
+        else:
+            # the fused kernel takes the product: no bias, no rotation, and the token's own key and value in place
+            qkv = torch.cat([q, k_dense[0][ctx - 1].reshape(1, -1).to(torch.bfloat16).to(DEV), v_dense[0][ctx - 1].reshape(1, -1).to(torch.bfloat16).to(DEV)], dim=1).contiguous()
+            fa.flash_decode_tma_fused(qkv, fa.DecodeFusion(None, None, 0, 1.0, True), out, k_pages, v_pages, tab, seq_of, positions,
+                                      1, nh, nkv, d, window, scale, 3, scratch, status)
+        return out, status.item()
+
+    whole, flags = run(table, None)
+    assert flags == 0
+    holed = table.clone()
+    holed[0, lost] = -1
+    out, flags = run(holed, None)
+    assert flags == 4
+    assert (out.view(1, nh, d).double().cpu() - ref).abs().max().item() < 2e-2
+    assert (out.float() - whole.float()).abs().max().item() > 1e-3  # 16 of 200 keys are gone: the result moved
+    behind, flags = run(holed, 60)  # a window of 60: keys 140 .. 199, page 5 is out of reach
+    assert flags == 0 and torch.isfinite(behind.float()).all()

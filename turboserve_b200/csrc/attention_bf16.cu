@@ -385,7 +385,18 @@ __device__ __forceinline__ unsigned cluster_map(unsigned local, int rank) {
 // cluster's results over distributed shared memory.  Every thread of the block calls it;
 // `active` is false for threads that hold no result (a producer warp).
 // ---------------------------------------------------------------------------------------------
-template <int D, bool CLUSTER>
+// SLOTS: how many partial results meet in the block's join area: one per consumer warp, and with
+// FLASH_WARPS + 1 one more that the caller has filled in before the call (rows of [16][D] floats
+// at decode_join_o(smem_raw) + FLASH_WARPS * 16 * D, their (max, sum) at decode_join_ml<D, SLOTS>
+// (smem_raw) + FLASH_WARPS * 16 * 2; a max of -inf gives the slot no weight and its rows are not read).
+template <int D> __device__ __forceinline__ float* decode_join_o(unsigned char* smem_raw) {
+  return reinterpret_cast<float*>(smem_raw);
+}
+template <int D, int SLOTS> __device__ __forceinline__ float* decode_join_ml(unsigned char* smem_raw) {
+  return reinterpret_cast<float*>(smem_raw) + SLOTS * 16 * D;
+}
+
+template <int D, bool CLUSTER, int SLOTS = FLASH_WARPS>
 __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2], float (&l)[2], unsigned char* smem_raw,
                                               bool active, int warp, int lane, int group, int kv_head, int token,
                                               int split, int num_splits, int num_heads, bf16* __restrict__ out,
@@ -393,8 +404,8 @@ __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2
                                               float* __restrict__ partial_ml) {
   const int g = lane >> 2, t = lane & 3;
   // each warp writes (m, l) per row and its O tile; then all read them
-  float* join_o = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
-  float* join_ml = join_o + FLASH_WARPS * 16 * D;                // [4][16][2]
+  float* join_o = decode_join_o<D>(smem_raw);                    // [SLOTS][16][D]
+  float* join_ml = decode_join_ml<D, SLOTS>(smem_raw);           // [SLOTS][16][2]
 #pragma unroll
   for (int h = 0; h < 2 && active; ++h) {
     float sum = l[h];
@@ -418,19 +429,20 @@ __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2
     const int row = idx / (D / 4), d0 = (idx % (D / 4)) * 4;
     float m_all = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < FLASH_WARPS; ++w) m_all = fmaxf(m_all, join_ml[(w * 16 + row) * 2]);
+    for (int w = 0; w < SLOTS; ++w) m_all = fmaxf(m_all, join_ml[(w * 16 + row) * 2]);
     float l_all = 0.0f, acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int w = 0; w < FLASH_WARPS; ++w) {
+    for (int w = 0; w < SLOTS; ++w) {
       const float mw = join_ml[(w * 16 + row) * 2];
-      const float wgt = mw == -INFINITY ? 0.0f : exp2f(mw - m_all);
+      if (mw == -INFINITY) continue;  // a slot without keys: no weight, and its rows may hold anything
+      const float wgt = exp2f(mw - m_all);
       l_all += join_ml[(w * 16 + row) * 2 + 1] * wgt;
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[e] += join_o[(w * 16 + row) * D + d0 + e] * wgt;
     }
     const int head = kv_head * group + row;
     if (CLUSTER) {
-      float* mine_o = join_ml + FLASH_WARPS * 16 * 2;  // [16][D] then [16][2], behind the warps' join area
+      float* mine_o = join_ml + SLOTS * 16 * 2;  // [16][D] then [16][2], behind the warps' join area
       float* mine_ml = mine_o + 16 * D;
       *reinterpret_cast<float4*>(mine_o + row * D + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       if (d0 == 0) {
@@ -456,7 +468,7 @@ __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2
     // every block of the cluster reaches this point (a padding token sends all of them away
     // together at the top); the barrier makes the partials visible across the cluster
     cluster_barrier();
-    const unsigned mine_o = smem_u32(join_ml + FLASH_WARPS * 16 * 2);
+    const unsigned mine_o = smem_u32(join_ml + SLOTS * 16 * 2);
     const unsigned mine_ml = mine_o + 16 * D * (unsigned)sizeof(float);
     for (int idx = active ? split * FLASH_THREADS + (int)threadIdx.x : group * (D / 4); idx < group * (D / 4); idx += num_splits * FLASH_THREADS) {
       const int row = idx / (D / 4), d0 = (idx % (D / 4)) * 4;
@@ -514,7 +526,7 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                     int table_stride, const int* __restrict__ seq_of_token,
                     const int* __restrict__ positions, int page_shift, int num_heads,
                     int num_kv_heads, int window, float scale_log2, int num_splits,
-                    float* __restrict__ partial_o, float* __restrict__ partial_ml) {
+                    float* __restrict__ partial_o, float* __restrict__ partial_ml, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger<8>();
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -576,12 +588,18 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
       q_hi[c] = q_rows[1] ? *reinterpret_cast<const uint4*>(q_rows[1] + 32 * c + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
     }
 
-    auto load_keys = [&](uint4 (&kr)[2][CHK], int i) {  // the i-th tile of this warp, into registers
+    // A key in range whose page is missing from the table (given back too early: a fault of whoever
+    // made the table) is masked out of the softmax and raises bit 4 of *status.  found[j] has bit
+    // 4 * r set when key 8 * j + r of the tile has its page.
+    auto load_keys = [&](uint4 (&kr)[2][CHK], unsigned (&found)[2], int i) {  // the i-th tile of this warp, into registers
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int key = begin + (warp + i * FLASH_WARPS) * WARP_TILE + 8 * j + g;
         bool ok = i < my_tiles && key < end;
         const int page = ok ? table[key >> page_shift] : -1;
+        const bool missing = ok && page < 0;
+        found[j] = __ballot_sync(0xffffffffu, !missing);
+        if (missing && t == 0 && status) atomicOr(status, 4);
         ok = ok && page >= 0;
         const bf16* row = k_pages + ((((size_t)(ok ? page : 0) << page_shift) + (key & page_mask)) * num_kv_heads + kv_head) * D + 8 * t;
 #pragma unroll
@@ -611,15 +629,16 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     };
 
     uint4 k0[2][CHK], k1[2][CHK], k2[2][CHK];
-    load_keys(k0, 0);
-    load_keys(k1, 1);
+    unsigned f0[2], f1[2], f2[2];
+    load_keys(k0, f0, 0);
+    load_keys(k1, f1, 1);
 #pragma unroll
     for (int s = 0; s < DECODE_STAGES - 1; ++s) {
       if (s < my_tiles) load_values(s);
       cp_async_commit();
     }
     for (int i = 0; i < my_tiles; ++i) {
-      load_keys(k2, i + 2);
+      load_keys(k2, f2, i + 2);
       if (i + DECODE_STAGES - 1 < my_tiles) load_values(i + DECODE_STAGES - 1);
       cp_async_commit();
       const int key0 = begin + (warp + i * FLASH_WARPS) * WARP_TILE;
@@ -635,6 +654,11 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
           mma16816(s[j], a_first, k0[j][c].x, k0[j][c].y);
           mma16816(s[j], a_second, k0[j][c].z, k0[j][c].w);
         }
+        if (f0[j] != 0xffffffffu) {  // element e of this thread is key 8 * j + 2 * t + (e & 1)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (!((f0[j] >> (4 * (2 * t + (e & 1)))) & 1u)) s[j][e] = -INFINITY;
+        }
       }
       int limit[2] = {min(rpos[0], end - 1), min(rpos[1], end - 1)};
       softmax_tile<D, 2>(s, o, m, l, key0, t, limit, rfirst, scale_log2);
@@ -649,6 +673,8 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
           k0[j][c] = k1[j][c];
           k1[j][c] = k2[j][c];
         }
+      f0[0] = f1[0]; f0[1] = f1[1];
+      f1[0] = f2[0]; f1[1] = f2[1];
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with its ring before the join reuses the memory
@@ -715,7 +741,35 @@ __device__ __forceinline__ unsigned dtma_offset(int r, int c) {
   return (unsigned)((c >> 3) * DTMA_HALF + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
-template <bool CLUSTER>
+// What the kernel needs to do the step before attention itself (FUSED): the raw q/k/v product of
+// the step's tokens, the bias, the rotation's constants, and the pages to append to.  The block
+// of a (request, kv head) adds the bias to its query heads and rotates them (fp32, rounded to
+// bfloat16 once, the arithmetic of rope_cache_write_kernel in layer_ops.cu bit for bit); the
+// block whose keys end at the token's own position does the same for the token's key, appends
+// key and value to the cache, and brings them into the softmax as one more partial result (a
+// score, a sum of 1, the value as the output), while the keys from the cache stop one position
+// earlier.  Nothing the kernel before wrote is needed for the keys and values of earlier
+// positions, so their copies are under way before the kernel waits for the projections.
+struct DecodeFusion {
+  const bf16* qkv;        // [tokens, qkv_stride]: query heads, then key heads, then value heads, 128 wide each
+  long long qkv_stride;
+  const float* bias;      // [(num_heads + 2 * num_kv_heads) * 128] or null
+  const float* inv_freq;  // [rotary_dim / 2] or null when rotary_dim == 0
+  int rotary_dim;         // even, at most 128; pairs (i, i + rotary_dim / 2) are rotated
+  float factor;           // positions are divided by it
+  bf16* k_pages;          // [pages, page_size, kv_heads, 128], appended to when write_kv
+  bf16* v_pages;
+  int write_kv;
+};
+
+#define DTMA_Q_STRIDE 136  // bf16 elements per row of the rotated queries in shared memory (272 bytes: no bank conflicts)
+
+__device__ __forceinline__ void dtma_rotate(float x1, float x2, float c, float s, float& o1, float& o2) {
+  o1 = __fmaf_rn(x1, c, -__fmul_rn(x2, s));  // the roundings of rope_rotate() in layer_ops.cu
+  o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
+}
+
+template <bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DTMA_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
@@ -723,27 +777,39 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                         int page_shift, int box_rows, int total_rows, int num_heads, int num_kv_heads,
                         int window, float scale_log2, int num_splits, float* __restrict__ partial_o,
-                        float* __restrict__ partial_ml, int* __restrict__ status) {
+                        float* __restrict__ partial_ml, int* __restrict__ status, const DecodeFusion fusion) {
   constexpr int D = 128;
-  pdl_wait();  // no early trigger: with it the decode step was 0.2 ms slower (3.42 against 3.21 ms)
+  constexpr int SLOTS = FUSED ? FLASH_WARPS + 1 : FLASH_WARPS;
+  if (!FUSED) pdl_wait();  // no early trigger: with it the decode step was 0.2 ms slower (3.42 against 3.21 ms)
   extern __shared__ unsigned char dtma_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * DTMA_STAGES];
   __shared__ int failed;
+  __shared__ unsigned gone_s[DTMA_STAGES];  // per stage: bit b set when box b lies on a page that is missing from the table
+  __shared__ __align__(16) bf16 q_s[FUSED ? 16 * DTMA_Q_STRIDE : 8];  // rotated queries, rows = heads of the group
+  __shared__ __align__(16) bf16 kv_s[FUSED ? 2 * D : 8];               // the token's own key (rotated), then value
+  __shared__ float cs_s[FUSED ? D : 2];                                 // cos, then sin, of the token's angles
 
   const int split = blockIdx.x, kv_head = blockIdx.y, token = blockIdx.z;
   const int seq = seq_of_token[token];
-  if (seq < 0) return;  // the same for every block of a cluster: nothing has been set up
+  if (seq < 0) {  // the same for every block of a cluster: nothing has been set up
+    if (FUSED) pdl_wait();
+    return;
+  }
   const int group = num_heads / num_kv_heads;
   const int pos = positions[token];
+  const int last_cached = FUSED ? pos - 1 : pos;  // the last key that comes from the cache
   const int kv_first = window > 0 ? max(0, pos - window + 1) : 0;
   const int tile_begin = kv_first / DTMA_KEYS, tile_end = pos / DTMA_KEYS + 1;
   const int per_split = (tile_end - tile_begin + num_splits - 1) / num_splits;
   const int my_begin = tile_begin + split * per_split;
   const int num_tiles = max(0, min(tile_end, my_begin + per_split) - my_begin);
+  // the part whose keys end at the token's own position: it appends the token's key and value
+  const bool owner = FUSED && split == (tile_end - 1 - tile_begin) / per_split;
   const int* table = block_table + (size_t)seq * table_stride;
   if (!CLUSTER && num_splits > 1 && num_tiles == 0) {
     // a part without keys (a short request in a batch that is cut for a long one): no weight in the
     // join, and nothing else to do (the same for every thread; nothing has been set up)
+    if (FUSED) pdl_wait();
     if ((int)threadIdx.x < group) {
       const size_t slot = ((size_t)token * num_heads + kv_head * group + threadIdx.x) * num_splits + split;
       partial_ml[slot * 2] = -INFINITY;
@@ -774,29 +840,37 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-  if (warp == FLASH_WARPS) {
-    // ---- producer: one lane per box (a page, or 64 keys of a larger page) ------------------------
-    const int page_size = 1 << page_shift;
-    const int boxes = DTMA_KEYS / box_rows;
-    for (int it = 0; it < num_tiles; ++it) {
+  // ---- producer (warp FLASH_WARPS): one lane per box (a page, or 64 keys of a larger page) ----------
+  const int page_size = 1 << page_shift;
+  const int boxes = DTMA_KEYS / box_rows;
+  bool producer_ok = true;
+  auto issue_tiles = [&](int from, int to) {
+    for (int it = from; it < to && producer_ok; ++it) {
       const int st = it % DTMA_STAGES;
       if (it >= DTMA_STAGES && !__all_sync(0xffffffffu, dtma_wait(empty0 + 8 * st, ((it / DTMA_STAGES) - 1) & 1, &failed))) {
         if (lane == 0) {
           failed = 1;
           if (status) atomicOr(status, 64);
         }
+        producer_ok = false;
         break;
       }
-      if (lane == 0) dtma_expect_tx(full0 + 8 * st, DTMA_STAGE_BYTES);
+      const int key = (my_begin + it) * DTMA_KEYS + lane * box_rows;
+      int row = total_rows;  // out of range: the box is filled with zeros
+      bool gone = false;
+      if (lane < boxes && key <= last_cached && key + box_rows > kv_first) {
+        const int page = table[key >> page_shift];
+        if (page >= 0) row = page * page_size + (key & (page_size - 1));
+        else gone = true;  // a page in reach of this block is missing: its keys get no weight
+      }
+      const unsigned gone_boxes = __ballot_sync(0xffffffffu, gone);
+      if (lane == 0) {
+        if (gone_boxes && status) atomicOr(status, 4);
+        gone_s[st] = gone_boxes;  // before the arrival below, which releases it to the consumers
+        dtma_expect_tx(full0 + 8 * st, DTMA_STAGE_BYTES);
+      }
       __syncwarp();
       if (lane < boxes) {
-        const int key = (my_begin + it) * DTMA_KEYS + lane * box_rows;
-        int row = total_rows;  // out of range: the box is filled with zeros
-        if (key <= pos && key + box_rows > kv_first) {
-          const int page = table[key >> page_shift];
-          if (page >= 0) row = page * page_size + (key & (page_size - 1));
-          else if (status) atomicOr(status, 4);  // a page in reach of this block is missing
-        }
         const unsigned dst = ring + st * DTMA_STAGE_BYTES + lane * box_rows * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -805,7 +879,108 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
       }
     }
-  } else if (num_tiles > 0) {
+  };
+
+  if (FUSED) {
+    // Before the wait: the first stages of keys and values (positions before the token's own: no
+    // kernel of this step has written them) and the token's angles.
+    const int ahead = min(num_tiles, DTMA_STAGES);
+    if (warp == FLASH_WARPS) issue_tiles(0, ahead);
+    const int half = fusion.rotary_dim / 2;
+    if ((int)threadIdx.x < half) {
+      float sn, cn;
+      sincosf(((float)pos / fusion.factor) * fusion.inv_freq[threadIdx.x], &sn, &cn);
+      cs_s[threadIdx.x] = cn;
+      cs_s[64 + threadIdx.x] = sn;
+    }
+    pdl_wait();
+    __syncthreads();
+    // rotated queries of the group's heads, and (owner) the token's key and value: rows
+    // 0 .. group - 1 are queries, row `group` the key, row `group + 1` the value
+    const bf16* x_row = fusion.qkv + (size_t)token * fusion.qkv_stride;
+    const int rows = owner ? group + 2 : group;
+    // Item (r, i), i < 64: elements i and i + 64 of row r (at most 18 rows: 16 heads, key, value).
+    // All loads of a thread are issued before the first result is needed: one trip to memory.
+    constexpr int ITEMS = (18 * 64 + DTMA_THREADS - 1) / DTMA_THREADS;
+    float xa[ITEMS], xb[ITEMS];
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) {
+      const int idx = threadIdx.x + u * DTMA_THREADS;
+      xa[u] = xb[u] = 0.0f;
+      if (idx < rows * 64) {
+        const int r = idx >> 6, i = idx & 63;
+        const int head = r < group ? kv_head * group + r : (r == group ? num_heads + kv_head : num_heads + num_kv_heads + kv_head);
+        const bf16* x = x_row + (size_t)head * D;
+        xa[u] = __bfloat162float(x[i]);
+        xb[u] = __bfloat162float(x[i + 64]);
+        if (fusion.bias) {
+          xa[u] += fusion.bias[(size_t)head * D + i];
+          xb[u] += fusion.bias[(size_t)head * D + i + 64];
+        }
+      }
+    }
+    // Elements e < half are rotated with e + half; elements from 2 * half on pass through.  With
+    // i < 64 <= D / 2 the pair of item i is (i, i + half) only when half == 64; for a narrower
+    // rotation the partner of element i lies in another item, so it is fetched again from the row.
+#pragma unroll
+    for (int u = 0; u < ITEMS; ++u) {
+      const int idx = threadIdx.x + u * DTMA_THREADS;
+      if (idx < rows * 64) {
+        const int r = idx >> 6, i = idx & 63;
+        const bool is_value = r == group + 1;
+        bf16* dst = r < group ? q_s + r * DTMA_Q_STRIDE : kv_s + (r - group) * D;
+        if (is_value || half == 0) {
+          dst[i] = __float2bfloat16_rn(xa[u]);
+          dst[i + 64] = __float2bfloat16_rn(xb[u]);
+        } else if (half == 64) {
+          float o1, o2;
+          dtma_rotate(xa[u], xb[u], cs_s[i], cs_s[64 + i], o1, o2);
+          dst[i] = __float2bfloat16_rn(o1);
+          dst[i + 64] = __float2bfloat16_rn(o2);
+        } else {
+          // a rotation narrower than the head: both of this item's elements on their own
+          const int head = r < group ? kv_head * group + r : num_heads + kv_head;
+          const bf16* x = x_row + (size_t)head * D;
+          const float* b = fusion.bias ? fusion.bias + (size_t)head * D : nullptr;
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const int e = i + 64 * which;
+            const float own = which ? xb[u] : xa[u];
+            float result = own;
+            if (e < 2 * half) {
+              const int partner = e < half ? e + half : e - half;
+              float other = __bfloat162float(x[partner]);
+              if (b) other += b[partner];
+              float o1, o2;
+              if (e < half) { dtma_rotate(own, other, cs_s[e], cs_s[64 + e], o1, o2); result = o1; }
+              else { dtma_rotate(other, own, cs_s[partner], cs_s[64 + partner], o1, o2); result = o2; }
+            }
+            dst[e] = __float2bfloat16_rn(result);
+          }
+        }
+      }
+    }
+    for (int idx = group * DTMA_Q_STRIDE + threadIdx.x; idx < 16 * DTMA_Q_STRIDE; idx += DTMA_THREADS)
+      q_s[idx] = __float2bfloat16_rn(0.0f);  // rows without a query
+    __syncthreads();
+    if (owner && fusion.write_kv && threadIdx.x < 32) {
+      // append: 16 threads copy the key, 16 the value, 16 bytes each
+      const int page = table[pos >> page_shift];
+      if (page < 0) {
+        if (threadIdx.x == 0 && status) atomicOr(status, 2);
+      } else {
+        const int which = threadIdx.x >> 4, chunk = threadIdx.x & 15;
+        bf16* pages = which ? fusion.v_pages : fusion.k_pages;
+        bf16* dst = pages + (((size_t)page * page_size + (pos & (page_size - 1))) * num_kv_heads + kv_head) * D;
+        *reinterpret_cast<uint4*>(dst + chunk * 8) = *reinterpret_cast<const uint4*>(kv_s + which * D + chunk * 8);
+      }
+    }
+    if (warp == FLASH_WARPS) issue_tiles(ahead, num_tiles);
+  } else if (warp == FLASH_WARPS) {
+    issue_tiles(0, num_tiles);
+  }
+
+  if (warp < FLASH_WARPS && num_tiles > 0) {
     // ---- consumers: warp w takes keys 16w .. 16w + 15 of every stage ------------------------------
     int rpos[2], rfirst[2];
     const bf16* q_rows[2];
@@ -813,9 +988,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int h = 0; h < 2; ++h) {
       const int row = g + 8 * h;
       const bool valid = row < group;
-      rpos[h] = valid ? pos : -1;
+      rpos[h] = valid ? last_cached : -1;
       rfirst[h] = kv_first;
-      q_rows[h] = valid ? q + (size_t)token * q_stride + (size_t)(kv_head * group + row) * D : nullptr;
+      if (FUSED) q_rows[h] = q_s + row * DTMA_Q_STRIDE;  // rows without a query are zero
+      else q_rows[h] = valid ? q + (size_t)token * q_stride + (size_t)(kv_head * group + row) * D : nullptr;
     }
     unsigned qf[D / 16][4];
     load_q_frags<D>(qf, q_rows[0], q_rows[1], t);
@@ -844,6 +1020,14 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         mma16816(sc[1], qf[kk], b[2], b[3]);
       }
       const int key0 = (my_begin + it) * DTMA_KEYS + 16 * warp;
+      const unsigned gone_boxes = gone_s[st];
+      if (gone_boxes) {  // element e of sc[i] is key 16 * warp + 8 * i + 2 * t + (e & 1) of the stage
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if ((gone_boxes >> ((16 * warp + 8 * i + 2 * t + (e & 1)) / box_rows)) & 1u) sc[i][e] = -INFINITY;
+      }
       softmax_tile<D, 2>(sc, o, m, l, key0, t, rpos, rfirst, scale_log2);
       unsigned a[4];
       a[0] = pack_bf16(sc[0][0], sc[0][1]);
@@ -867,8 +1051,33 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int st = 0; st < DTMA_STAGES; ++st)
       for (int i = 0; i < 4096 && !dtma_try_wait(full0 + 8 * st, 0) && !dtma_try_wait(full0 + 8 * st, 1); ++i) {}
   }
-  decode_finish<D, CLUSTER>(o, m, l, ring_ptr, warp < FLASH_WARPS, warp, lane, group, kv_head, token, split, num_splits,
-                            num_heads, out, out_stride, partial_o, partial_ml);
+  if (FUSED && warp == FLASH_WARPS) {
+    // the token's own key and value as one more partial result: score, a sum of 1, the value
+    float* extra_o = decode_join_o<D>(ring_ptr) + FLASH_WARPS * 16 * D;
+    float* extra_ml = decode_join_ml<D, SLOTS>(ring_ptr) + FLASH_WARPS * 16 * 2;
+    float kd[4], vd[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      kd[e] = __bfloat162float(kv_s[4 * lane + e]);
+      vd[e] = __bfloat162float(kv_s[D + 4 * lane + e]);
+    }
+    for (int row = 0; row < 16; ++row) {
+      float score = -INFINITY;
+      if (owner && row < group) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dot += __bfloat162float(q_s[row * DTMA_Q_STRIDE + 4 * lane + e]) * kd[e];
+        score = warp_sum(dot) * scale_log2;
+        *reinterpret_cast<float4*>(extra_o + row * D + 4 * lane) = make_float4(vd[0], vd[1], vd[2], vd[3]);
+      }
+      if (lane == 0) {
+        extra_ml[row * 2] = score;
+        extra_ml[row * 2 + 1] = score == -INFINITY ? 0.0f : 1.0f;
+      }
+    }
+  }
+  decode_finish<D, CLUSTER, SLOTS>(o, m, l, ring_ptr, warp < FLASH_WARPS, warp, lane, group, kv_head, token, split,
+                                   num_splits, num_heads, out, out_stride, partial_o, partial_ml);
 }
 
 // Join the splits of a decode step: one block per (token, head), one thread per dim.
@@ -957,7 +1166,8 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, long long
                          const bf16* k_pages, const bf16* v_pages, const int* block_table,
                          int table_stride, const int* seq_of_token, const int* positions,
                          int num_tokens, int shift, int num_heads, int num_kv_heads, int window,
-                         float scale_log2, int num_splits, float* scratch, bool cluster, cudaStream_t stream) {
+                         float scale_log2, int num_splits, float* scratch, bool cluster, int* status,
+                         cudaStream_t stream) {
   const size_t kv_smem = (size_t)FLASH_WARPS * DECODE_STAGES * 16 * D * sizeof(bf16);
   const size_t join_smem = (size_t)(FLASH_WARPS + 1) * 16 * (D + 2) * sizeof(float);  // the warps' join area, then the block's partials
   const size_t smem = kv_smem > join_smem ? kv_smem : join_smem;
@@ -967,7 +1177,7 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, long long
     ts_launch_cluster(flash_decode_kernel<D, true>, dim3(num_splits, num_kv_heads, num_tokens), dim3(FLASH_THREADS), smem,
                       stream, num_splits, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                       seq_of_token, positions, shift, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                      (float*)nullptr, (float*)nullptr);
+                      (float*)nullptr, (float*)nullptr, status);
     return ts_launch_status();
   }
   cudaFuncSetAttribute(flash_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -976,9 +1186,9 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, long long
   dim3 grid(num_splits, num_kv_heads, num_tokens);
   ts_launch(flash_decode_kernel<D, false>, dim3(grid), dim3(FLASH_THREADS), smem, stream, 
       q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_of_token, positions,
-      shift, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml);
-  int status = ts_launch_status();
-  if (status || num_splits == 1) return status;
+      shift, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status);
+  int code = ts_launch_status();
+  if (code || num_splits == 1) return code;
   dim3 join_grid(num_heads, num_tokens);
   ts_launch(flash_decode_join_kernel<D>, dim3(join_grid), dim3(D), 0, stream, out, out_stride, seq_of_token, num_heads,
                                                             num_splits, partial_o, partial_ml);
@@ -993,7 +1203,7 @@ static int flash_decode_checked(const void* q, long long q_stride, void* out, lo
                                 int table_stride, const int* seq_of_token, const int* positions,
                                 int num_tokens, int page_size, int num_heads, int num_kv_heads,
                                 int head_dim, int window, float scale, int num_splits, float* scratch,
-                                bool allow_cluster, cudaStream_t stream) {
+                                bool allow_cluster, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int bad = check_common(q, q_stride, out, out_stride, head_dim, num_heads, num_kv_heads, page_size);
   if (bad) return bad;
@@ -1009,11 +1219,11 @@ static int flash_decode_checked(const void* q, long long q_stride, void* out, lo
     return launch_decode<128>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
                               (const bf16*)v_pages, block_table, table_stride, seq_of_token, positions,
                               num_tokens, shift, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                              scratch, cluster, stream);
+                              scratch, cluster, status, stream);
   return launch_decode<64>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
                            (const bf16*)v_pages, block_table, table_stride, seq_of_token, positions,
                            num_tokens, shift, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                           scratch, cluster, stream);
+                           scratch, cluster, status, stream);
 }
 
 TS_EXPORT int ts_flash_decode(const void* q, long long q_stride, void* out, long long out_stride,
@@ -1021,10 +1231,10 @@ TS_EXPORT int ts_flash_decode(const void* q, long long q_stride, void* out, long
                               int table_stride, const int* seq_of_token, const int* positions,
                               int num_tokens, int page_size, int num_heads, int num_kv_heads,
                               int head_dim, int window, float scale, int num_splits, float* scratch,
-                              cudaStream_t stream) {
+                              int* status, cudaStream_t stream) {
   return flash_decode_checked(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                               seq_of_token, positions, num_tokens, page_size, num_heads, num_kv_heads, head_dim,
-                              window, scale, num_splits, scratch, true, stream);
+                              window, scale, num_splits, scratch, true, status, stream);
 }
 
 // ---- the TMA-fed decode kernel's host side -------------------------------------------------------
@@ -1060,12 +1270,14 @@ static int dtma_make_map(CUtensorMap* map, const void* pages, long long rows, lo
 
 // Decode steps with head size 128 and pages of 4 to 2^30 tokens (a power of two), keys and values
 // fetched by TMA.  Splits and scratch as for ts_flash_decode; num_pages is the pool's size.
-TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,
-                                  const void* k_pages, const void* v_pages, long long num_pages,
-                                  const int* block_table, int table_stride, const int* seq_of_token,
-                                  const int* positions, int num_tokens, int page_size, int num_heads,
-                                  int num_kv_heads, int head_dim, int window, float scale, int num_splits,
-                                  float* scratch, int* status, cudaStream_t stream) {
+template <bool FUSED>
+static int flash_decode_tma_checked(const void* q, long long q_stride, void* out, long long out_stride,
+                                    const void* k_pages, const void* v_pages, long long num_pages,
+                                    const int* block_table, int table_stride, const int* seq_of_token,
+                                    const int* positions, int num_tokens, int page_size, int num_heads,
+                                    int num_kv_heads, int head_dim, int window, float scale, int num_splits,
+                                    float* scratch, int* status, const DecodeFusion& fusion, bool allow_cluster,
+                                    cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int bad = check_common(q, q_stride, out, out_stride, head_dim, num_heads, num_kv_heads, page_size);
   if (bad) return bad;
@@ -1074,7 +1286,7 @@ TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, 
   if (((uintptr_t)q & 3) || (q_stride & 1)) return TS_ERR_ALIGN;
   if (((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return TS_ERR_ALIGN;
   if (num_splits < 1 || num_splits > 65535 || num_kv_heads > 65535 || num_tokens > 65535) return TS_ERR_SIZE;
-  const bool cluster = num_splits >= 2 && num_splits <= DECODE_CLUSTER_MAX;
+  const bool cluster = allow_cluster && num_splits >= 2 && num_splits <= DECODE_CLUSTER_MAX;
   if (num_splits > 1 && !cluster && (scratch == nullptr || ((uintptr_t)scratch & 15))) return TS_ERR_ARGUMENT;
   const long long rows = num_pages * page_size;
   if (rows <= 0 || rows >= (1ll << 31) - 256) return TS_ERR_SIZE;
@@ -1090,22 +1302,67 @@ TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, 
   float* partial_ml = scratch ? scratch + (size_t)num_tokens * num_heads * num_splits * head_dim : nullptr;
   const dim3 grid(num_splits, num_kv_heads, num_tokens);
   if (cluster) {
-    cudaFuncSetAttribute(flash_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
-    ts_launch_cluster(flash_decode_tma_kernel<true>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, num_splits, map_k, map_v,
-                      (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token,
+    cudaFuncSetAttribute(flash_decode_tma_kernel<true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
+    ts_launch_cluster(flash_decode_tma_kernel<true, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, num_splits, map_k,
+                      map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token,
                       positions, shift, box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                      (float*)nullptr, (float*)nullptr, status);
+                      (float*)nullptr, (float*)nullptr, status, fusion);
     return ts_launch_status();
   }
-  cudaFuncSetAttribute(flash_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
-  ts_launch(flash_decode_tma_kernel<false>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, map_k, map_v, (const bf16*)q,
-            q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token, positions, shift, box_rows,
-            (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status);
+  cudaFuncSetAttribute(flash_decode_tma_kernel<false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
+  ts_launch(flash_decode_tma_kernel<false, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, map_k, map_v,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token, positions, shift,
+            box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
+            fusion);
   code = ts_launch_status();
   if (code || num_splits == 1) return code;
   ts_launch(flash_decode_join_kernel<128>, dim3(num_heads, num_tokens), dim3(128), 0, stream, (bf16*)out, out_stride,
             seq_of_token, num_heads, num_splits, partial_o, partial_ml);
   return ts_launch_status();
+}
+
+TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,
+                                  const void* k_pages, const void* v_pages, long long num_pages,
+                                  const int* block_table, int table_stride, const int* seq_of_token,
+                                  const int* positions, int num_tokens, int page_size, int num_heads,
+                                  int num_kv_heads, int head_dim, int window, float scale, int num_splits,
+                                  float* scratch, int* status, cudaStream_t stream) {
+  DecodeFusion none;
+  memset(&none, 0, sizeof(none));
+  return flash_decode_tma_checked<false>(q, q_stride, out, out_stride, k_pages, v_pages, num_pages, block_table,
+                                         table_stride, seq_of_token, positions, num_tokens, page_size, num_heads,
+                                         num_kv_heads, head_dim, window, scale, num_splits, scratch, status, none, true, stream);
+}
+
+// The same, with the step before attention done by the kernel itself (see DecodeFusion): qkv is
+// the raw product [tokens, qkv_stride] (query heads, key heads, value heads), bias fp32 or null,
+// inv_freq fp32 [rotary_dim / 2]; the token's key and value are appended to the pages when
+// write_kv is set.  Nothing of qkv is changed.  Without allow_cluster two to DECODE_CLUSTER_MAX
+// splits also meet in scratch (which must then be given) and are joined by the second kernel.
+TS_EXPORT int ts_flash_decode_tma_fused(const void* qkv, long long qkv_stride, const float* bias, const float* inv_freq,
+                                        int rotary_dim, float factor, int write_kv, void* out, long long out_stride,
+                                        void* k_pages, void* v_pages, long long num_pages, const int* block_table,
+                                        int table_stride, const int* seq_of_token, const int* positions,
+                                        int num_tokens, int page_size, int num_heads, int num_kv_heads, int head_dim,
+                                        int window, float scale, int num_splits, float* scratch, int* status,
+                                        int allow_cluster, cudaStream_t stream) {
+  if (rotary_dim < 0 || rotary_dim > 128 || (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr)) return TS_ERR_SIZE;
+  if (!(factor > 0.0f)) return TS_ERR_ARGUMENT;
+  if (qkv_stride < (long long)(num_heads + 2 * num_kv_heads) * 128) return TS_ERR_SIZE;
+  DecodeFusion fusion;
+  fusion.qkv = (const bf16*)qkv;
+  fusion.qkv_stride = qkv_stride;
+  fusion.bias = bias;
+  fusion.inv_freq = inv_freq;
+  fusion.rotary_dim = rotary_dim;
+  fusion.factor = factor;
+  fusion.k_pages = (bf16*)k_pages;
+  fusion.v_pages = (bf16*)v_pages;
+  fusion.write_kv = write_kv;
+  return flash_decode_tma_checked<true>(qkv, qkv_stride, out, out_stride, k_pages, v_pages, num_pages, block_table,
+                                        table_stride, seq_of_token, positions, num_tokens, page_size, num_heads,
+                                        num_kv_heads, head_dim, window, scale, num_splits, scratch, status, fusion,
+                                        allow_cluster != 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1151,5 +1408,5 @@ TS_EXPORT int ts_flash_decode_static(const void* q, long long q_stride, void* ou
   // always the scratch path: the splits meet in the static array, never in a cluster
   return flash_decode_checked(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                               seq_of_token, positions, num_tokens, page_size, num_heads, num_kv_heads, head_dim,
-                              window, scale, num_splits, scratch, false, stream);
+                              window, scale, num_splits, scratch, false, nullptr, stream);
 }

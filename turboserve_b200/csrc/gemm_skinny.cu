@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
                    const __nv_bfloat16* __restrict__ w, long long ldw,
                    const float* __restrict__ bias, TOut* __restrict__ c, long long ldc, int m,
-                   int n, int k) {
+                   int n, int k, int early_trigger) {
   constexpr int ROW_TILES = SKINNY_WARPS / KSPLIT;
   __shared__ float partial[KSPLIT > 1 ? SKINNY_WARPS : 1][MT * 4 * 32];
 
@@ -108,7 +108,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
   uint4 lo0[U], hi0[U], lo1[U], hi1[U];
   issue(lo0, hi0, chunk_begin);  // weights: nothing before this kernel writes them
   pdl_wait();                    // activations come from the kernel before
-  pdl_trigger<2>();
+  if (early_trigger) pdl_trigger<2>();  // not when the kernel after this one is launched as clusters (slow to launch early)
   for (int chunk = chunk_begin; chunk < chunk_end; chunk += 2 * U) {
     issue(lo1, hi1, chunk + U);
     compute(lo0, hi0, chunk);
@@ -153,14 +153,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
 template <int MT, typename TOut>
 static int launch_skinny(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* w,
                          long long ldw, const float* bias, TOut* c, long long ldc, int m, int n,
-                         int k, int ksplit, cudaStream_t stream) {
+                         int k, int ksplit, int early_trigger, cudaStream_t stream) {
   const int rows_per_block = 16 * SKINNY_WARPS / ksplit;
   const int grid = (n + rows_per_block - 1) / rows_per_block;
   switch (ksplit) {
-    case 1: ts_launch(gemm_skinny_kernel<MT, 1, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k); break;
-    case 2: ts_launch(gemm_skinny_kernel<MT, 2, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k); break;
-    case 4: ts_launch(gemm_skinny_kernel<MT, 4, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k); break;
-    case 8: ts_launch(gemm_skinny_kernel<MT, 8, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k); break;
+    case 1: ts_launch(gemm_skinny_kernel<MT, 1, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k, early_trigger); break;
+    case 2: ts_launch(gemm_skinny_kernel<MT, 2, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k, early_trigger); break;
+    case 4: ts_launch(gemm_skinny_kernel<MT, 4, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k, early_trigger); break;
+    case 8: ts_launch(gemm_skinny_kernel<MT, 8, TOut>, dim3(grid), dim3(SKINNY_WARPS * 32), 0, stream, a, lda, w, ldw, bias, c, ldc, m, n, k, early_trigger); break;
     default: return TS_ERR_ARGUMENT;
   }
   return ts_launch_status();
@@ -169,18 +169,20 @@ static int launch_skinny(const __nv_bfloat16* a, long long lda, const __nv_bfloa
 template <typename TOut>
 static int dispatch_skinny(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* w,
                            long long ldw, const float* bias, TOut* c, long long ldc, int m, int n,
-                           int k, int ksplit, cudaStream_t stream) {
-  if (m <= 8) return launch_skinny<1, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, stream);
-  if (m <= 16) return launch_skinny<2, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, stream);
-  if (m <= 32) return launch_skinny<4, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, stream);
-  return launch_skinny<8, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, stream);
+                           int k, int ksplit, int early_trigger, cudaStream_t stream) {
+  if (m <= 8) return launch_skinny<1, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, early_trigger, stream);
+  if (m <= 16) return launch_skinny<2, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, early_trigger, stream);
+  if (m <= 32) return launch_skinny<4, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, early_trigger, stream);
+  return launch_skinny<8, TOut>(a, lda, w, ldw, bias, c, ldc, m, n, k, ksplit, early_trigger, stream);
 }
 
+// early_trigger: whether the kernel lets the one after it in the stream be set up as soon as it
+// has its own inputs (programmatic dependent launch); 0 holds the next kernel back until this one ends.
 // ksplit: 0 lets the entry point choose (the smallest of 1, 2, 4, 8 that gives every SM two
 // blocks, given the number of SMs of the current device); otherwise one of 1, 2, 4, 8.
 TS_EXPORT int ts_gemm_skinny(int out_dtype, const void* a, long long lda, const void* w,
                              long long ldw, const float* bias, void* c, long long ldc, int m,
-                             int n, int k, int ksplit, int num_sms, cudaStream_t stream) {
+                             int n, int k, int ksplit, int num_sms, int early_trigger, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (m > 64) return TS_ERR_SIZE;
   if (k < 8 || k % 8) return TS_ERR_SIZE;
@@ -198,8 +200,8 @@ TS_EXPORT int ts_gemm_skinny(int out_dtype, const void* a, long long lda, const 
   const __nv_bfloat16* ap = (const __nv_bfloat16*)a;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
   if (out_dtype == TS_BF16)
-    return dispatch_skinny<__nv_bfloat16>(ap, lda, wp, ldw, bias, (__nv_bfloat16*)c, ldc, m, n, k, ksplit, stream);
+    return dispatch_skinny<__nv_bfloat16>(ap, lda, wp, ldw, bias, (__nv_bfloat16*)c, ldc, m, n, k, ksplit, early_trigger, stream);
   if (out_dtype == TS_F32)
-    return dispatch_skinny<float>(ap, lda, wp, ldw, bias, (float*)c, ldc, m, n, k, ksplit, stream);
+    return dispatch_skinny<float>(ap, lda, wp, ldw, bias, (float*)c, ldc, m, n, k, ksplit, early_trigger, stream);
   return TS_ERR_DTYPE;
 }

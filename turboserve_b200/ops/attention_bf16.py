@@ -13,6 +13,7 @@ launch shape serves a captured graph at any context length.
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -81,8 +82,11 @@ def decode_scratch_floats(num_tokens: int, num_heads: int, num_splits: int, head
 
 
 def flash_decode(q, out, k_pages, v_pages, block_table, seq_of_token, positions, num_tokens, num_heads, num_kv_heads,
-                 head_dim, window, scale, num_splits, scratch) -> None:
-    """Attention for a decode step; ``scratch`` is fp32 of ``decode_scratch_floats(...)`` elements."""
+                 head_dim, window, scale, num_splits, scratch, status=None) -> None:
+    """Attention for a decode step; ``scratch`` is fp32 of ``decode_scratch_floats(...)`` elements.
+
+    A page that is missing from the table inside a request's visible keys is masked out and
+    raises bit 4 of ``status`` (int32, one element) when that is given."""
     _common(q, out, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim)
     _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
     if num_splits > CLUSTER_MAX_SPLITS:
@@ -91,11 +95,11 @@ def flash_decode(q, out, k_pages, v_pages, block_table, seq_of_token, positions,
             raise KernelError("flash_decode: scratch is too small")
     fn = _fn("attention_bf16", "ts_flash_decode",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
               block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens, k_pages.shape[1], num_heads,
               num_kv_heads, head_dim, int(window or 0), float(scale), num_splits,
-              _ptr(scratch if num_splits > CLUSTER_MAX_SPLITS else None), _stream()), "flash_decode",
+              _ptr(scratch if num_splits > CLUSTER_MAX_SPLITS else None), _ptr(status), _stream()), "flash_decode",
            launches=2 if num_splits > CLUSTER_MAX_SPLITS else 1)  # more splits than a cluster holds: a join kernel follows
 
 
@@ -123,10 +127,82 @@ def flash_decode_tma(q, out, k_pages, v_pages, block_table, seq_of_token, positi
            launches=2 if num_splits > CLUSTER_MAX_SPLITS else 1)
 
 
+FUSED_CLUSTER = os.environ.get("TURBOSERVE_B200_FUSED_CLUSTER", "1") != "0"
+FUSED_DECODE = os.environ.get("TURBOSERVE_B200_FUSED_DECODE", "0") != "0"
+"""With 1, decode steps let the TMA-fed attention kernel add the bias, rotate queries and keys and
+append to the cache itself (one launch less a layer). Off by default: measured inside a captured
+decode step at the 7B sizes (batch 8, context 4,096) the step takes 3.35 ms that way against 3.28 ms
+with the rotation kernel, whose launch and angles already hide behind the product before it, while
+the attention kernel, launched as clusters, cannot be set up ahead of time without costing more
+than it saves (3.70 ms), and joining its parts through scratch instead of a cluster costs 3.44 ms."""
+
+
+@dataclass
+class DecodeFusion:
+    """The step before attention, handed to the decode kernel instead of being run on its own:
+    the bias of the fused q/k/v product, the rotation's constants, and whether to append."""
+
+    bias: torch.Tensor | None
+    inv_freq: torch.Tensor | None
+    rotary_dim: int
+    factor: float
+    write: bool
+
+
+def can_fuse_decode(qkv: torch.Tensor, k_pages: torch.Tensor, batch, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, rotary_dim: int) -> bool:
+    """Whether this step's attention can take the raw q/k/v product (:func:`flash_decode_tma_fused`):
+    a decode-only bfloat16 step whose shape the TMA-fed kernel takes, with the mixer's own keys and values."""
+    return (FUSED_DECODE and TMA_DECODE and qkv.dtype == torch.bfloat16 and batch.is_decode_only and scale > 0
+            and tma_decode_supports(head_dim, k_pages.shape[1], num_heads // num_kv_heads)
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and qkv.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim
+            and 0 <= rotary_dim <= head_dim and rotary_dim % 2 == 0)
+
+
+def flash_decode_tma_fused(qkv, fusion: DecodeFusion, out, k_pages, v_pages, block_table, seq_of_token, positions, num_tokens,
+                           num_heads, num_kv_heads, head_dim, window, scale, num_splits, scratch, status=None) -> None:
+    """Decode attention straight from the raw q/k/v product: bias, rotation and cache append happen in the kernel."""
+    _common(qkv, out, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim)
+    _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] < width:
+        raise KernelError("flash_decode_tma_fused: qkv is narrower than its heads")
+    if fusion.bias is not None:
+        _need(fusion.bias, torch.float32, "bias")
+        if fusion.bias.numel() != width:
+            raise KernelError("flash_decode_tma_fused: bias length does not match the projected heads")
+    if fusion.rotary_dim:
+        _need(fusion.inv_freq, torch.float32, "inv_freq")
+        if fusion.inv_freq.numel() * 2 != fusion.rotary_dim:
+            raise KernelError("flash_decode_tma_fused: inv_freq must hold rotary_dim / 2 values")
+    cluster = FUSED_CLUSTER and 2 <= num_splits <= CLUSTER_MAX_SPLITS
+    if num_splits > 1 and not cluster:
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < decode_scratch_floats(num_tokens, num_heads, num_splits, head_dim):
+            raise KernelError("flash_decode_tma_fused: scratch is too small")
+    fn = _fn("attention_bf16", "ts_flash_decode_tma_fused",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+              c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+              c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(qkv), qkv.stride(0), _ptr(fusion.bias), _ptr(fusion.inv_freq if fusion.rotary_dim else None),
+              int(fusion.rotary_dim), float(fusion.factor), int(bool(fusion.write)), _ptr(out), out.stride(0),
+              _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table), block_table.stride(0), _ptr(seq_of_token),
+              _ptr(positions), num_tokens, k_pages.shape[1], num_heads, num_kv_heads, head_dim, int(window or 0),
+              float(scale), num_splits, _ptr(scratch if num_splits > 1 and not cluster else None), _ptr(status),
+              int(cluster or FUSED_CLUSTER), _stream()), "flash_decode_tma_fused",
+           launches=2 if num_splits > 1 and not cluster else 1)
+
+
 def paged_attention_bf16(q, out, k_pages, v_pages, block_table, batch, num_heads, num_kv_heads, head_dim, window,
-                         scale, ctx) -> bool:
-    """Run the tensor-core kernel that fits the step; returns False if the shape is refused."""
+                         scale, ctx, fusion: DecodeFusion | None = None) -> bool:
+    """Run the tensor-core kernel that fits the step; returns False if the shape is refused.
+
+    With ``fusion`` (only after :func:`can_fuse_decode` said yes) ``q`` is the raw q/k/v product."""
     group = num_heads // num_kv_heads
+    if fusion is not None:
+        _decode_tokens(q, out, k_pages, v_pages, block_table, batch, 0, batch.num_tokens, num_heads, num_kv_heads, head_dim,
+                       window, scale, ctx, fusion)
+        return True
     if not scale > 0:
         return False  # the tiled kernel keeps its running maximum in unscaled units
     decode = batch.is_decode_only and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
@@ -166,7 +242,8 @@ def paged_attention_bf16(q, out, k_pages, v_pages, block_table, batch, num_heads
     return True
 
 
-def _decode_tokens(q, out, k_pages, v_pages, block_table, batch, first, n, num_heads, num_kv_heads, head_dim, window, scale, ctx) -> None:
+def _decode_tokens(q, out, k_pages, v_pages, block_table, batch, first, n, num_heads, num_kv_heads, head_dim, window, scale, ctx,
+                   fusion: DecodeFusion | None = None) -> None:
     """Tokens ``first .. first + n`` of the batch, each against the keys of its request up to its position."""
     if first:
         q, out = q[first:], out[first:]
@@ -182,9 +259,12 @@ def _decode_tokens(q, out, k_pages, v_pages, block_table, batch, first, n, num_h
     # (buffers may not grow once decode graphs have been captured)
     bound = num_heads * (head_dim + 2) * (n + SKEW_SPLIT_ROOM * ((2 * sms) // num_kv_heads) + 1)
     scratch = ctx.buffer("attn.decode_scratch", (bound,), torch.float32)
-    if TMA_DECODE and tma_decode_supports(head_dim, k_pages.shape[1], group):
+    if fusion is not None:
+        flash_decode_tma_fused(q, fusion, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads,
+                               num_kv_heads, head_dim, window, scale, splits, scratch, ctx.status)
+    elif TMA_DECODE and tma_decode_supports(head_dim, k_pages.shape[1], group):
         flash_decode_tma(q, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads,
                          num_kv_heads, head_dim, window, scale, splits, scratch, ctx.status)
     else:
         flash_decode(q, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads,
-                     num_kv_heads, head_dim, window, scale, splits, scratch)
+                     num_kv_heads, head_dim, window, scale, splits, scratch, ctx.status)

@@ -40,10 +40,12 @@ TC_MIN_FEATURES = 16384
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
-           rows: int | None = None, ctx=None) -> torch.Tensor:
+           rows: int | None = None, ctx=None, early_trigger: bool = True) -> torch.Tensor:
     """``out[:rows] = x[:rows] @ weight.T (+ bias)``; ``bias`` is float32.
 
     ``ctx`` (a step context) lends scratch and the status word to kernels that want them.
+    ``early_trigger=False`` asks a kernel of this package not to let the next kernel of the stream
+    start ahead of its own end (for a next kernel that is slow to launch that way).
     """
     m = x.shape[0] if rows is None else rows
     if m == 0:
@@ -61,7 +63,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch
         from . import skinny
 
         if -(-n // 16) <= 2 * skinny.num_sms(x.device):
-            skinny.gemm_skinny(x, weight, out, bias, m)
+            skinny.gemm_skinny(x, weight, out, bias, m, early_trigger=early_trigger)
             return out
     xs, os_ = x[:m], out[:m]
     if out.dtype == torch.bfloat16 and bias is None:

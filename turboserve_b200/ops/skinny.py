@@ -20,7 +20,7 @@ def num_sms(device: torch.device) -> int:
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
-                m: int | None = None, ksplit: int = 0) -> None:
+                m: int | None = None, ksplit: int = 0, early_trigger: bool = True) -> None:
     """``out[:m] = a[:m] @ w.T (+ bias)``; bfloat16 inputs, bfloat16 or float32 output, m <= 64."""
     _need(a, torch.bfloat16, "a"); _need(w, torch.bfloat16, "w"); _need(out, None, "out")
     if a.dim() != 2 or w.dim() != 2 or out.dim() != 2 or a.shape[1] != w.shape[1] or out.shape[1] != w.shape[0]:
@@ -34,6 +34,6 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
             raise KernelError("gemm_skinny: bias length does not match the output width")
     fn = _fn("gemm_skinny", "ts_gemm_skinny",
              [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
-              c_int, c_int, c_void_p])
+              c_int, c_int, c_int, c_void_p])
     _check(fn(kernels.dtype_code(out.dtype), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
-              out.stride(0), rows, w.shape[0], a.shape[1], ksplit, num_sms(a.device), _stream()), "gemm_skinny")
+              out.stride(0), rows, w.shape[0], a.shape[1], ksplit, num_sms(a.device), int(early_trigger), _stream()), "gemm_skinny")

@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import PartSpec
-from ..ops.attention import paged_attention
+from ..ops.attention import decode_fusion, paged_attention
 from ..ops.linear import linear
 from .base import MIXERS, POSITIONS, Mixer, PagedKVNeed, ParamSpec, register_mixer
 from .rope import NoPosition
@@ -86,13 +86,19 @@ class PagedAttention(Mixer):
         n = batch.num_tokens
         table = batch.block_tables[cache.group]
         qkv = ctx.buffer("attn.qkv", (n, self.qkv_width))
-        linear(x, self.qkv, qkv, None, n, ctx)
-        self.position.apply(qkv, self.qkv_b, self.num_heads, self.proj_kv_heads, self.head_dim, ctx, cache,
-                            cache.writes and not self.shares_cache)
+        write = cache.writes and not self.shares_cache
+        # a decode step may leave bias, encoding and append to the attention kernel itself
+        fusion = None if self.shares_cache else decode_fusion(
+            qkv, cache.k_pages, batch, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.qkv_b,
+            self.position.fused_rotation(), write)
+        # that kernel is launched as thread-block clusters, which are slow to set up ahead of time
+        linear(x, self.qkv, qkv, None, n, ctx, early_trigger=fusion is None)
+        if fusion is None:
+            self.position.apply(qkv, self.qkv_b, self.num_heads, self.proj_kv_heads, self.head_dim, ctx, cache, write)
         attended = ctx.buffer("attn.attended", (n, self.num_heads * self.head_dim))
         paged_attention(
             qkv, attended, cache.k_pages, cache.v_pages, table, batch, self.num_heads, self.num_kv_heads,
-            self.head_dim, self.window, self.scale, ctx,
+            self.head_dim, self.window, self.scale, ctx, fusion,
         )
         out = ctx.buffer("attn.out", (n, self.hidden_size))
         linear(attended, self.out_w, out, self.out_b, n, ctx)

@@ -171,6 +171,16 @@ class PositionEncoding:
     rotary_dim = 0
     factor = 1.0
 
+    def fused_rotation(self) -> tuple[torch.Tensor | None, int, float] | None:
+        """``(inv_freq, rotary_dim, factor)`` when :meth:`apply` is the default one, else ``None``.
+
+        A mixer may hand these constants to a kernel that does the whole of :meth:`apply` itself
+        (decode attention does); an encoding that overrides :meth:`apply` is always called.
+        """
+        if type(self).apply is not PositionEncoding.apply:
+            return None
+        return self.inv_freq, self.rotary_dim, self.factor
+
     def check(self, head_dim: int) -> None:
         """Refuse a head size the encoding cannot act on (called once, when the mixer is built)."""
         if self.rotary_dim > head_dim:
