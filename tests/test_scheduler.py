@@ -159,7 +159,7 @@ def test_recompute_cut_by_the_budget_samples_only_at_its_end():
     for _ in range(7):
         run_step(s)
     assert a.num_tokens == 12
-    s._preempt(a, SchedulerOutput(), set())
+    s._send_back(a, set(), SchedulerOutput())
     assert a.num_computed_tokens == 0 and a.num_tokens == 12
     plan = run_step(s)
     assert [(i.start, i.num_new_tokens, i.samples) for i in plan.scheduled] == [(0, 8, False)]

@@ -51,9 +51,6 @@
 // Replaces the reference's per-sequence gather + SDPA (src/turboserve/engine/model/
 // attention.py:184-209).
 #include <cuda.h>
-#ifdef ATC_TRACE
-#include <cstdio>
-#endif
 
 #include "common.cuh"
 
@@ -410,26 +407,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     float m = -INFINITY;  // the maximum the exponentials are taken against (raw score units)
     float2 l2 = make_float2(0.0f, 0.0f);
     bool ok = true;
-#ifdef ATC_TRACE
-    long long t_phase[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t_last = clock64();
-    int ready_s = 0, ready_o = 0;
-#define ATC_MARK(k) { const long long now = clock64(); t_phase[k] += now - t_last; t_last = now; }
-#else
-#define ATC_MARK(k)
-#endif
     for (int j = 0; j < num_tiles; ++j) {
-#ifdef ATC_TRACE
-      ready_s += atc_try_wait(s_full + 8 * (j & 1), (j >> 1) & 1) ? 1 : 0;
-#endif
       ok = __all_sync(0xffffffffu, atc_wait(s_full + 8 * (j & 1), (j >> 1) & 1, &failed));
-      ATC_MARK(0)
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int key0 = (tile_begin + j) * ATC_KEYS + part * ATC_COLS;
       const bool masked = key0 + ATC_COLS - 1 > my_pos || key0 < my_first;
       float v[ATC_COLS];
       atc_ld32(tmem + (j & 1) * ATC_KEYS + part * ATC_COLS + lane_base, v);
-      ATC_MARK(1)
       if (masked) {
 #pragma unroll
         for (int i = 0; i < ATC_COLS; ++i) {
@@ -456,7 +441,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
       for (int other = 0; other < ATC_SPLIT; ++other) mx = fmaxf(mx, row_pair[other][r]);
       atc_arrive(pair_read);
-      ATC_MARK(2)
       // The reference maximum moves only when the new one is far above it (2^8 in the exponent):
       // until then the exponentials may exceed one, which fp32 sums and bfloat16 P hold easily,
       // and the O row in tensor memory needs no rescaling.
@@ -480,12 +464,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         packed[i] = atc_pack(pr.x, pr.y);
       }
       l2 = __fadd2_rn(__fadd2_rn(sums[0], sums[1]), __fadd2_rn(sums[2], sums[3]));
-      ATC_MARK(3)
       if (j > 0) {
         // the O product of the tile before has read P (one buffer) and completed O
-#ifdef ATC_TRACE
-        ready_o += atc_try_wait(o_full, (j - 1) & 1) ? 1 : 0;
-#endif
         ok = __all_sync(0xffffffffu, atc_wait(o_full, (j - 1) & 1, &failed));
         if (!ok) break;
         if (__any_sync(0xffffffffu, move)) {
@@ -501,7 +481,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      ATC_MARK(4)
 #pragma unroll
       for (int i = 0; i < ATC_COLS / 8; ++i) {  // 16-byte chunks of 8 keys; a row of P is 8 chunks
         const int chunk = part * (ATC_COLS / 8) + i;
@@ -512,13 +491,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       atc_arrive(p_ready);
-      ATC_MARK(5)
     }
-#ifdef ATC_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0)
-      printf("tiles %d: S ready on arrival %d times, O %d times; cycles per tile: wait S %lld, ld %lld, max+exchange %lld, exp %lld, wait O+rescale %lld, store P %lld\n", num_tiles, ready_s, ready_o,
-             t_phase[0] / num_tiles, t_phase[1] / num_tiles, t_phase[2] / num_tiles, t_phase[3] / num_tiles, t_phase[4] / num_tiles, t_phase[5] / num_tiles);
-#endif
     if (ok && num_tiles > 0) {
       ok = __all_sync(0xffffffffu, atc_wait(o_full, (num_tiles - 1) & 1, &failed));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

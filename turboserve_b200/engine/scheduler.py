@@ -117,7 +117,6 @@ class Scheduler:
                        sampling=sampling)
         seq.seed = int(sampling.seed if sampling.seed is not None else (seed if seed is not None else seq.seq_id))
         budget = self.config.max_num_batched_tokens
-        longest = seq.num_prompt_tokens + sampling.max_tokens
         if not self.cache.fits_at_all(seq.num_prompt_tokens, budget):
             raise ValueError(
                 f"request {request_id!r} has {seq.num_prompt_tokens} prompt tokens, more than the cache can "
@@ -128,7 +127,6 @@ class Scheduler:
                 f"request {request_id!r} has {seq.num_tokens} tokens but the step budget is {budget} and "
                 "chunked prefill is disabled"
             )
-        del longest
         self._next_seq_id += 1
         seq.timing.t_arrival = time.perf_counter() if arrival is None else arrival
         self._by_request[request_id] = seq
@@ -156,8 +154,8 @@ class Scheduler:
         out = SchedulerOutput()
         tokens_left = self.config.max_num_batched_tokens
         seqs_left = self.config.max_num_seqs
-        scheduled_ids: set[int] = set()
-        preempted_now: set[int] = set()
+        in_step: set[int] = set()        # seq ids that already have their share of this step
+        evicted: set[int] = set()        # seq ids preempted while this step was put together
         prefills: list[ScheduledSeq] = []
         decodes: list[ScheduledSeq] = []
 
@@ -176,7 +174,7 @@ class Scheduler:
             seq.num_computed_tokens = end
             tokens_left -= num_new
             seqs_left -= 1
-            scheduled_ids.add(seq.seq_id)
+            in_step.add(seq.seq_id)
             (prefills if item.is_prefill else decodes).append(item)
 
         # 1. running requests
@@ -190,7 +188,7 @@ class Scheduler:
                 continue
             if not self.config.enable_chunked_prefill and num_new < seq.num_uncomputed_tokens:
                 continue
-            if not self._make_room(seq, num_new, scheduled_ids, out, preempted_now):
+            if not self._grow_or_evict(seq, num_new, in_step, evicted, out):
                 continue
             emit(seq, num_new)
 
@@ -207,7 +205,7 @@ class Scheduler:
                 self.finish(seq, FinishReason.LENGTH, now=stamp)
                 out.dropped.append(seq)
                 continue
-            if seq.seq_id in preempted_now:
+            if seq.seq_id in evicted:
                 break
             num_new = min(tokens_left, seq.num_uncomputed_tokens)
             if not self.config.enable_chunked_prefill and num_new < seq.num_uncomputed_tokens:
@@ -285,29 +283,32 @@ class Scheduler:
         self.num_decode_tokens += len(items)
         return out
 
-    def _make_room(self, seq: Sequence, num_new: int, scheduled_ids: set[int], out: SchedulerOutput,
-                   preempted_now: set[int]) -> bool:
+    def _grow_or_evict(self, seq: Sequence, num_new: int, in_step: set[int], evicted: set[int],
+                       out: SchedulerOutput) -> bool:
+        """Make sure ``seq`` can take pages for ``num_new`` more tokens; ``False`` if it had to go itself.
+
+        While its page pools cannot serve it, the running request that was admitted last, is not
+        part of this step and is not ``seq`` gives everything back and is computed again later
+        (``src/turboserve/engine/core/scheduler.py:748-802`` chooses the same victim); when no
+        such request is left, ``seq`` is the one that goes.
+        """
         while not self.cache.can_grow(seq.request_id, num_new):
-            victim = self._pick_victim(scheduled_ids, seq)
-            if victim is None:
-                self._preempt(seq, out, preempted_now)
+            others = [r for r in self._running
+                      if r is not seq and r.seq_id not in in_step and r.status is SeqStatus.RUNNING]
+            loser = max(others, key=lambda r: r.seq_id) if others else seq
+            self._send_back(loser, evicted, out)
+            if loser is seq:
                 return False
-            self._preempt(victim, out, preempted_now)
         return True
 
-    def _pick_victim(self, scheduled_ids: set[int], requester: Sequence) -> Sequence | None:
-        candidates = [s for s in self._running
-                      if s is not requester and s.seq_id not in scheduled_ids and s.status is SeqStatus.RUNNING]
-        if not candidates:
-            return None
-        return max(candidates, key=lambda s: s.seq_id)
-
-    def _preempt(self, seq: Sequence, out: SchedulerOutput, preempted_now: set[int]) -> None:
+    def _send_back(self, seq: Sequence, evicted: set[int], out: SchedulerOutput) -> None:
+        """Recompute preemption of one running request: pages and slot back, progress to zero,
+        tokens kept, to the end of the queue that is served before new arrivals."""
         self.cache.release(seq.request_id)
         seq.reset_for_recompute()
         self._running.remove(seq)
         self._preempted.append(seq)
-        preempted_now.add(seq.seq_id)
+        evicted.add(seq.seq_id)
         out.preempted.append(seq)
         self.num_preemptions += 1
 
@@ -337,12 +338,11 @@ class Scheduler:
         return True
 
     def _detach(self, seq: Sequence) -> None:
-        if seq in self._running:
-            self._running.remove(seq)
-        elif seq in self._preempted:
-            self._preempted.remove(seq)
-        elif seq in self._waiting:
-            self._waiting.remove(seq)
+        """Take a finished request out of whichever queue holds it, and out of the index."""
+        for queue in (self._running, self._preempted, self._waiting):
+            if seq in queue:
+                queue.remove(seq)
+                break
         self._by_request.pop(seq.request_id, None)
 
     def reset(self) -> None:
