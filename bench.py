@@ -247,7 +247,38 @@ def decode_end_to_end(runner, config, batch: int, context_end: int, steps: int, 
     return elapsed, produced, h2d, 4 * runner.token_buffer.numel()
 
 
-def prefill_run(runner, config, tokens: int, repeats: int = 6, warmup: int = 3):
+def prefill_end_to_end(runner, config, tokens: int, repeats: int = 5):
+    """A prompt of ``tokens`` tokens through ``LLMEngine.step()`` to its first token: host token ids in
+    (scheduler, packing, pinned host-to-device copy), one step, the sampled id read back. Median and best, seconds."""
+    import torch
+
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    engine_config = EngineConfig(
+        model="(injected)", dtype="bfloat16", max_model_len=tokens + PAGE,
+        scheduler=SchedulerConfig(max_num_seqs=1, max_num_batched_tokens=tokens, block_size=PAGE,
+                                  num_blocks=runner.groups[0].num_pages))
+    engine = LLMEngine(engine_config, runner=runner)
+    generator = torch.Generator().manual_seed(5)
+    sampling = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+    times = []
+    for i in range(repeats + 2):
+        prompt = torch.randint(0, config.vocab_size, (tokens,), generator=generator).tolist()
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        engine.add_request(f"prefill-{i}", prompt, sampling)
+        outputs = engine.step()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - started
+        if len(outputs) != 1 or not outputs[0].finished:
+            raise RuntimeError("the prompt did not run in one step")
+        if i >= 2:
+            times.append(elapsed)
+    engine.close()
+    return statistics.median(times), min(times)
+
+
+def prefill_run(runner, config, tokens: int, repeats: int = 7, warmup: int = 3):
     import torch
 
     from turboserve_b200.engine.batch import RequestSlice
@@ -266,7 +297,7 @@ def prefill_run(runner, config, tokens: int, repeats: int = 6, warmup: int = 3):
         if i >= warmup:
             times.append(begin.elapsed_time(end) / 1000.0)
     runner.check_status()
-    return min(times)
+    return statistics.median(times), min(times)
 
 
 def prefill_flops(config, tokens: int) -> float:
@@ -388,6 +419,35 @@ def reference_arm(args, shape_name: str, shape_raw: dict) -> int:
     return 0
 
 
+def fp32_products() -> int:
+    """The true 32-bit path's matrix product (FFMA, no tensor cores) at the 7B layer's shapes: one JSON line."""
+    import torch
+
+    from turboserve_b200.ops.linear import linear
+
+    shapes = {"qkv": (3584, 4608), "o": (3584, 3584), "gate_up": (3584, 37888), "down": (18944, 3584)}
+    line = {"what": "float32 FFMA product (gemm_simt.cu), Qwen2-7B layer shapes", "unit": "TFLOP/s (rows 2048) and GB/s of weights (rows 8)"}
+    for name, (k, n) in shapes.items():
+        w = torch.randn(n, k, device="cuda")
+        for rows in (2048, 8):
+            x = torch.randn(rows, k, device="cuda")
+            out = torch.empty(rows, n, device="cuda")
+            for _ in range(2):
+                linear(x, w, out)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(3):
+                linear(x, w, out)
+            end.record()
+            torch.cuda.synchronize()
+            seconds = begin.elapsed_time(end) / 3e3
+            line[f"{name}_rows{rows}_ms"] = round(seconds * 1e3, 3)
+            line[f"{name}_rows{rows}"] = round(2 * rows * k * n / seconds / 1e12, 2) if rows > 8 else round(4 * k * n / seconds / 1e9, 1)
+        del w
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -405,6 +465,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT,
                         help="context length of the decode runs (the headline is 4096; others are for sweeps)")
     parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
+    parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                         help="run three eager steps of that kind and exit (a small case for a profiler)")
     args = parser.parse_args()
@@ -424,6 +485,8 @@ def main() -> int:
 
     from turboserve_b200.ops import kernels
 
+    if args.fp32_products:
+        return fp32_products()
     if args.one_step:
         return one_step(args.one_step, args.layers, args.batch, args.shape)
     if args.scenario:
@@ -458,12 +521,27 @@ def main() -> int:
         for b in (1, 64):
             s, _, _ = decode_on_device(runner, b, context, args.steps, args.warmup)
             points[f"decode_b{b}"] = round(b * args.steps / s, 1)
-        t = prefill_run(runner, config, 2048)
+            s, n, _, _ = decode_end_to_end(runner, config, b, context, args.steps, args.warmup)
+            points[f"e2e_decode_b{b}"] = round(n / s, 1)
+        t, best = prefill_run(runner, config, 2048)
         flops = prefill_flops(config, 2048)
-        prefill = {"value": round(2048 / t, 1), "tokens": 2048, "ms": round(t * 1e3, 3),
+        # value, ms and frac are the median of the repeats; best_ms is the fastest of them
+        prefill = {"value": round(2048 / t, 1), "tokens": 2048, "ms": round(t * 1e3, 3), "best_ms": round(best * 1e3, 3),
                    "frac": round(flops / t / (peaks["bf16_tflops"] * 1e12), 4), "peak": of}
         if "bf16_tflops_sustained" in peaks:  # the step is long enough to run under the power cap
             prefill["frac_of_sustained"] = round(flops / t / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+        e2e_t, e2e_best = prefill_end_to_end(runner, config, 2048)
+        prefill["e2e_value"] = round(2048 / e2e_t, 1)
+        prefill["e2e_ms"] = round(e2e_t * 1e3, 3)
+        prefill["e2e_best_ms"] = round(e2e_best * 1e3, 3)
+    # what a batch pays that is the first of its size to be lopsided (decode attention cut finer:
+    # another graph): a warm-up step, a synchronisation and the capture. Even batches of every
+    # size were captured when the engine was built.
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    runner._capture(next(b for b in runner._graph_buckets if b >= args.batch), 16)
+    torch.cuda.synchronize()
+    first_lopsided_ms = (time.perf_counter() - started) * 1e3
 
     sampler.stop()
     clocks = sampler.summary(mark0, mark1)
@@ -497,6 +575,7 @@ def main() -> int:
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": of,
                      "bytes_per_step": int(step_bytes)},
         "points": points,
+        "graphs": {"captured_at_start": runner.num_graph_captures - 1, "first_lopsided_step_extra_ms": round(first_lopsided_ms, 2)},
         "impl": "ours",
     }
     if prefill is not None:

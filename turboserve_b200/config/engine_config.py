@@ -133,6 +133,11 @@ class EngineConfig(BaseModel):
     cuda_graphs: bool = True
     """Replay decode-only steps from captured CUDA graphs (bfloat16 path)."""
 
+    capture_graphs_at_start: bool = True
+    """Capture the decode graphs of every batch size when the engine is built, instead of when a
+    batch size is first met in the middle of serving (lopsided batches, whose attention is cut
+    finer, are still captured when first met)."""
+
     overlap_decode: bool = True
     """Launch the next decode step before the tokens of the current one have been read, when that
     step is certain to hold the same requests one token on (``LLMEngine.step``)."""

@@ -84,6 +84,8 @@ class LLMEngine:
             pages = min(g.num_pages for g in self.runner.groups)
             longest = min(config.max_model_len or pages * config.block_size, pages * config.block_size)
             self.runner.enable_graphs(config.scheduler.max_num_seqs, longest, config.scheduler.max_num_batched_tokens)
+            if config.capture_graphs_at_start and hasattr(self.runner, "capture_decode_graphs"):
+                self.runner.capture_decode_graphs()
 
     # -- context manager ---------------------------------------------------------------------
 

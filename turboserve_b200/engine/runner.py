@@ -92,6 +92,7 @@ class ModelRunner:
         self._pinned_next = 0
         self.num_steps = 0
         self.num_graph_replays = 0
+        self.num_graph_captures = 0
         self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, StaticBatch, torch.Tensor]] = {}
         self._graph_buckets: list[int] = []
         self._graph_widths: list[int] = []
@@ -186,30 +187,56 @@ class ModelRunner:
         return True
 
     @torch.inference_mode()
+    def _capture(self, bucket: int, skew: int, slices: Sequence[RequestSlice] = (),
+                 device_tokens: torch.Tensor | None = None):
+        """Capture the decode graph of ``bucket`` requests at lopsidedness ``skew``.
+
+        The kernels' grids depend on the batch size and the class alone, so the capture may run on
+        a batch of padding tokens (which touch no page) as well as on the step that first needs it.
+        """
+        static = StaticBatch(bucket, bucket, self._graph_widths, self.device)
+        static.load_decode(slices)
+        static.batch.decode_skew = skew
+        if device_tokens is not None:
+            static.batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.run(static.batch)  # warm-up outside the capture: compiles, cuBLAS handles
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.run(static.batch)
+        entry = (graph, static, logits)
+        self._graphs[(bucket, skew)] = entry
+        self.num_graph_captures += 1
+        # the warm-up and the capture ran the step's side effects on this very batch already:
+        # the cache holds these tokens; replaying once more writes the same values again
+        return entry
+
+    def capture_decode_graphs(self, skew_classes: Sequence[int] = (1,)) -> int:
+        """Capture the decode graphs of every batch-size bucket for the given classes now, so that
+        no request meets a capture (a warm-up step, a synchronisation and the capture itself) in
+        the middle of serving. Lopsided batches of other classes are still captured when first met.
+        Returns how many graphs were captured."""
+        before = self.num_graph_captures
+        for bucket in self._graph_buckets:
+            for skew in skew_classes:
+                if (bucket, skew) not in self._graphs:
+                    self._capture(bucket, skew)
+        self.status.zero_()
+        return self.num_graph_captures - before
+
+    @torch.inference_mode()
     def _replay_decode(self, slices: Sequence[RequestSlice], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         bucket = next(b for b in self._graph_buckets if b >= len(slices))
         # the kernels' grids are part of a graph, and decode attention sizes its grid by how lopsided
-        # the batch is: one graph per (batch size, class), captured when first needed
+        # the batch is: one graph per (batch size, class), captured at start-up or when first needed
         key = (bucket, skew_class([piece.start_position + 1 for piece in slices]))
         entry = self._graphs.get(key)
         if entry is None:
-            static = StaticBatch(bucket, bucket, self._graph_widths, self.device)
-            static.load_decode(slices)
-            if device_tokens is not None:
-                static.batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
-            stream = torch.cuda.Stream(device=self.device)
-            stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(stream):
-                self.run(static.batch)  # warm-up outside the capture: compiles, cuBLAS handles
-            torch.cuda.current_stream(self.device).wait_stream(stream)
-            torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.run(static.batch)
-            entry = (graph, static, logits)
-            self._graphs[key] = entry
-            # the warm-up and the capture ran the step's side effects on this very batch already:
-            # the cache holds these tokens; replaying once more writes the same values again
+            entry = self._capture(bucket, key[1], slices, device_tokens)
         graph, static, logits = entry
         static.load_decode(slices)
         if device_tokens is not None:
