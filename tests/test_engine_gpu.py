@@ -135,43 +135,50 @@ def test_temperature_sampling_matches_the_plain_sampler(model_folders, name):
 
 
 def test_bfloat16_sampled_rows_match_the_plain_sampler_on_the_engines_own_logits(model_folders):
-    """Temperature, top-k, top-p and a penalty in bfloat16, graphs and steps launched ahead included:
-    every sampled id is what the plain sampler draws from the very row of logits the engine's
-    sampler was given (exact ids), so a fault of the sampler cannot hide behind bfloat16 rounding."""
+    """Temperature, top-k, top-p and a penalty in bfloat16, with decode steps replayed from graphs that
+    end with the sampler (options by state slot) and launched ahead: every sampled id is what the
+    plain sampler draws from the very row of logits the step produced (exact ids), so a fault of
+    the sampler, of the slot arrays or of the token's index cannot hide behind bfloat16 rounding."""
     from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
-    from turboserve_b200.sampling.sampler import Sampler
-
-    class Recording(Sampler):
-        def __init__(self, device):
-            super().__init__(device)
-            self.seen = []
-
-        def sample_device(self, logits, rows, out=None):
-            tokens, logprobs = super().sample_device(logits, rows, out)
-            self.seen.append((logits[: len(rows)].clone(), [(r.params, r.seed, r.counter, list(r.history)) for r in rows], tokens.clone()))
-            return tokens, logprobs
 
     config, _ = P.read_model_folder(model_folders["D"])
     prompts = prompts_for(config, [9, 31, 60, 4], seed=12)
     options = [dict(temperature=0.7, seed=11), dict(temperature=1.2, top_k=20, top_p=0.9, seed=5),
                dict(temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3), dict(temperature=1.0, top_p=0.95)]
-    sampler = Recording("cuda")
     engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="bfloat16", seed=3, scheduler=SchedulerConfig(
-        max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)), sampler=sampler)
+        max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)))
+    launched, checked, in_graph = [], [0], [0]
+    run_step, process = engine.runner.step, engine._process
+
+    def recording_step(slices, device_tokens=None):
+        logits = run_step(slices, device_tokens)
+        launched.append(None if logits is None else logits.clone())
+        in_graph[0] += int(engine.runner.sampled_in_graph)
+        return logits
+
+    def checking_process(plan, result):
+        logits = launched.pop(0)  # steps are processed in the order they were launched
+        if result is not None:
+            for row, seq, token in zip(logits.cpu(), plan.sampling_seqs(), result.token_ids):
+                if seq.is_finished:
+                    continue
+                params = seq.sampling
+                expect, _ = P.sample_token(row, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
+                                           repetition_penalty=params.repetition_penalty, history=seq.token_ids, seed=seq.seed,
+                                           counter=seq.num_output_tokens)
+                assert token == expect, (seq.request_id, seq.num_output_tokens, token, expect)
+                checked[0] += 1
+        return process(plan, result)
+
+    engine.runner.step, engine._process = recording_step, checking_process
     with engine:
+        assert engine.runner.graph_sampler is engine.sampler and engine.sampler.slots is not None
         # the request with a penalty (which no step can be launched ahead of) ends early; the others go on
         lengths = [14, 14, 6, 14]
         outputs = engine.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True, **o) for n, o in zip(lengths, options)])
-        assert engine.stats()["num_overlapped_steps"] > 0 and engine.runner.num_graph_replays > 0
+        assert engine.stats()["num_overlapped_steps"] > 0 and engine.runner.num_graph_replays > 0 and in_graph[0] > 0
     assert [o.output_tokens for o in outputs] == lengths
-    checked = 0
-    for logits, rows, tokens in sampler.seen:
-        for row, (params, seed, counter, history), token in zip(logits.cpu(), rows, tokens.tolist()):
-            expect, _ = P.sample_token(row, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
-                                       repetition_penalty=params.repetition_penalty, history=history, seed=seed, counter=counter)
-            assert token == expect, (counter, token, expect)
-            checked += 1
-    assert checked == sum(lengths)
+    assert checked[0] == sum(lengths)
 
 
 def test_long_decoding_through_many_pages_and_a_window(model_folders):

@@ -841,3 +841,51 @@ def test_decode_kernels_mask_and_flag_a_page_that_is_missing_inside_the_visible_
     assert (out.float() - whole.float()).abs().max().item() > 1e-3  # 16 of 200 keys are gone: the result moved
     behind, flags = run(holed, 60)  # a window of 60: keys 140 .. 199, page 5 is out of reach
     assert flags == 0 and torch.isfinite(behind.float()).all()
+
+
+@pytest.mark.parametrize("vocab, chunks", [(777, 1), (777, 8), (152064, 8), (1000, 3)])
+def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row(vocab, chunks):
+    """``sample_slots`` finds a row's options through its state slot, derives the index of the token
+    being generated from the request's length, skips padding rows, and cuts rows that need one
+    pass into several blocks: the ids equal those of ``sample`` given the same options row by row."""
+    from turboserve_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(vocab)
+    num_slots, rows = 12, 9
+    logits = (torch.randn(rows, vocab, generator=gen) * 3).to(DEV)
+    logits[2, 5] = logits[2, 700] = logits[2].max() + 1.0  # a tie for the greedy row: the lower id wins in every cut
+    # per slot: temperature, top_k, top_p, seed, prompt length
+    slot_opts = {3: (0.0, 0, 1.0, 1, 4), 7: (0.8, 0, 1.0, 22, 9), 0: (1.3, 40, 1.0, 5, 1), 11: (0.6, 0, 0.9, 8, 30),
+                 5: (1.0, 25, 0.7, 13, 2), 9: (0.0, 10, 0.5, 3, 7), 2: (2.0, 0, 1.0, 77, 100), 6: (0.9, 0, 1.0, 1 << 40, 3)}
+    row_slot = [3, 7, 9, 0, 11, 5, 2, 6, 4]
+    row_seq = [0, 1, 2, 3, 4, 5, 6, 7, -1]  # the last row is padding
+    row_context = [10, 9, 50, 17, 33, 2, 164, 5, 0]
+    temperature = torch.zeros(num_slots); top_p = torch.ones(num_slots)
+    top_k = torch.zeros(num_slots, dtype=torch.int32); prompt_len = torch.zeros(num_slots, dtype=torch.int32)
+    seed = torch.zeros(num_slots, dtype=torch.int64)
+    for slot, (t, k, p, s, plen) in slot_opts.items():
+        temperature[slot], top_k[slot], top_p[slot], seed[slot], prompt_len[slot] = t, k, p, s, plen
+    work = torch.empty(rows * vocab, device=DEV)
+    partial = torch.zeros(rows * (2 * chunks + 1), dtype=torch.int32, device=DEV)
+    dev = lambda t: t.to(DEV)
+    for _ in range(2):  # twice: the counters in `partial` are left at zero
+        tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        kernels.sample_slots(logits, work, tokens, rows, temperature=dev(temperature), top_k=dev(top_k), top_p=dev(top_p),
+                             seed=dev(seed), prompt_len=dev(prompt_len), row_slot=dev(torch.tensor(row_slot, dtype=torch.int32)),
+                             row_seq=dev(torch.tensor(row_seq, dtype=torch.int32)), row_context=dev(torch.tensor(row_context, dtype=torch.int32)),
+                             partial=partial, chunks=chunks)
+        live = rows - 1
+        by_row = torch.empty(live, dtype=torch.int32, device=DEV)
+        opts = [slot_opts[s] for s in row_slot[:live]]
+        kernels.sample(logits[:live], work, by_row, temperature=dev(torch.tensor([o[0] for o in opts])),
+                       top_k=dev(torch.tensor([o[1] for o in opts], dtype=torch.int32)), top_p=dev(torch.tensor([o[2] for o in opts])),
+                       seed=dev(torch.tensor([o[3] for o in opts], dtype=torch.int64)),
+                       counter=dev(torch.tensor([c - o[4] for c, o in zip(row_context, opts)], dtype=torch.int32)))
+        assert tokens[:live].tolist() == by_row.tolist()
+        assert tokens[live].item() == -7 and tokens[2].item() == 5
+        assert int(partial.view(rows, -1)[:, 0].abs().sum()) == 0
+    # and against the plain sampler
+    for r in (0, 1, 4, 7):
+        t, k, p, s, plen = slot_opts[row_slot[r]]
+        expect, _ = P.sample_token(logits[r].cpu(), temperature=t, top_k=k, top_p=p, seed=s, counter=row_context[r] - plen)
+        assert tokens[r].item() == expect

@@ -16,6 +16,22 @@
 //
 // `work` ([rows, vocab] fp32) is scratch owned by the caller; its contents are dead after
 // the call.
+//
+// A row may be cut into `chunks` parts along the vocabulary, one block each (grid = rows x
+// chunks), when all it needs is one pass: a greedy row, or a draw with neither top-k nor top-p
+// (no penalty, no log-probability either).  Every part finds its own best (value, id), leaves
+// it in `partial`, and the part that finishes last (an atomic count per row, no waiting) picks
+// among them; "larger value, lower id on ties" does not depend on the order.  A row that needs
+// the filters is worked by its first block alone.  `partial` holds rows * (2 * chunks + 1) words
+// and its counters must be zero before the first call; the kernel leaves them zero.
+//
+// Options may also be looked up by state slot (row_slot != null): the arrays temperature, top_k,
+// top_p and seed are then indexed by row_slot[row], a row whose row_seq[row] is negative is
+// padding and is skipped, and the index of the token being generated is
+// row_context[row] - prompt_len[row_slot[row]] (the request's length after the step minus its
+// prompt), so nothing on the device has to be advanced from step to step.  A slot whose
+// temperature is negative is left alone (its request wants what this path does not do: a
+// penalty over its history, a log-probability) and its row's token is not written.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
@@ -128,7 +144,9 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
               const float* __restrict__ top_p, const float* __restrict__ penalty,
               const unsigned long long* __restrict__ seed, const unsigned int* __restrict__ counter,
               const int* __restrict__ history, const int* __restrict__ history_start,
-              int* __restrict__ tokens, float* __restrict__ logprobs) {
+              int* __restrict__ tokens, float* __restrict__ logprobs, const int* __restrict__ row_slot,
+              const int* __restrict__ row_seq, const int* __restrict__ row_context,
+              const int* __restrict__ prompt_len, int* __restrict__ partial) {
   pdl_wait();
   pdl_trigger();
   __shared__ ArgMax arg_scratch[33];
@@ -147,13 +165,62 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   __shared__ unsigned int sel_remaining;
 
   const int row = blockIdx.x;
+  if (row_seq && row_seq[row] < 0) return;  // a padding row of a fixed-size batch
+  const int opt = row_slot ? row_slot[row] : row;  // where this row's options are
   const float* x = logits + (size_t)row * logits_stride;
   float* w = work + (size_t)row * vocab;
   const int tid = threadIdx.x;
+  const float temp = temperature ? temperature[opt] : 0.0f;
+  if (row_slot && temp < 0.0f) return;  // a slot marked "not from here": its row is sampled by another call
+  const float pen = penalty && !row_slot ? penalty[row] : 1.0f;
+  const bool need_lse = logprobs != nullptr;
+  const int k = top_k ? top_k[opt] : 0;
+  const float p_option = top_p ? top_p[opt] : 1.0f;
+  const unsigned long long sd = seed ? seed[opt] : 0ull;
+  const unsigned int ctr = row_slot ? (unsigned int)(row_context[row] - prompt_len[opt]) : (counter ? counter[row] : 0u);
+
+  // -- one pass is enough: greedy, or a draw without filters ----------------------------------
+  const int chunks = gridDim.y;
+  const bool one_pass = pen == 1.0f && !need_lse && (temp == 0.0f || (!(k > 0 && k < vocab) && !(p_option < 1.0f)));
+  if (one_pass && partial != nullptr) {
+    const int per = (vocab + chunks - 1) / chunks;
+    const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+    ArgMax pick{-INFINITY, 0x7fffffff};
+    if (temp == 0.0f) {
+      for (int i = lo + tid; i < hi; i += blockDim.x) pick = better(pick, ArgMax{x[i], i});
+    } else {
+      for (int i = lo + tid; i < hi; i += blockDim.x) {
+        const float v = x[i] / temp;
+        if (v == -INFINITY) continue;
+        const float u = sample_uniform(sd, ctr, (unsigned int)i);
+        pick = better(pick, ArgMax{v - logf(-logf(u)), i});
+      }
+    }
+    pick = block_argmax(pick, arg_scratch);
+    if (chunks == 1) {
+      if (tid == 0) tokens[row] = pick.index;
+      return;
+    }
+    int* mine = partial + (size_t)row * (2 * chunks + 1);
+    if (tid == 0) {
+      mine[1 + 2 * blockIdx.y] = __float_as_int(pick.value);
+      mine[2 + 2 * blockIdx.y] = pick.index;
+      __threadfence();
+      if (atomicAdd(&mine[0], 1) == chunks - 1) {  // every other part has left its best behind
+        __threadfence();
+        ArgMax all{-INFINITY, 0x7fffffff};
+        for (int c = 0; c < chunks; ++c)
+          all = better(all, ArgMax{__int_as_float(__ldcg(&mine[1 + 2 * c])), __ldcg(&mine[2 + 2 * c])});
+        tokens[row] = all.index;
+        mine[0] = 0;
+      }
+    }
+    return;
+  }
+  if (blockIdx.y != 0) return;  // a row that needs more than one pass is its first block's alone
 
   // -- repetition penalty ---------------------------------------------------------------
   for (int i = tid; i < vocab; i += blockDim.x) w[i] = x[i];
-  const float pen = penalty ? penalty[row] : 1.0f;
   if (pen != 1.0f && history_start) {
     __syncthreads();
     const int h0 = history_start[row], h1 = history_start[row + 1];
@@ -166,9 +233,6 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
     }
   }
   __syncthreads();
-
-  const float temp = temperature ? temperature[row] : 0.0f;
-  const bool need_lse = logprobs != nullptr;
 
   // -- greedy ---------------------------------------------------------------------------
   ArgMax best{-INFINITY, 0x7fffffff};
@@ -197,7 +261,6 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   __syncthreads();
 
   // -- top-k ----------------------------------------------------------------------------------
-  const int k = top_k ? top_k[row] : 0;
   if (k > 0 && k < vocab) {
     if (tid == 0) { sel_prefix = 0; sel_remaining = (unsigned int)k; }
     __syncthreads();
@@ -249,7 +312,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   }
 
   // -- top-p ----------------------------------------------------------------------------------
-  const float p_keep = top_p ? top_p[row] : 1.0f;
+  const float p_keep = p_option;
   if (p_keep < 1.0f) {
     float mx = -INFINITY;
     for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, w[i]);
@@ -345,8 +408,6 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   }
 
   // -- draw -------------------------------------------------------------------------------------
-  const unsigned long long sd = seed ? seed[row] : 0ull;
-  const unsigned int ctr = counter ? counter[row] : 0u;
   ArgMax pick{-INFINITY, 0x7fffffff};
   for (int i = tid; i < vocab; i += blockDim.x) {
     const float v = w[i];
@@ -379,9 +440,33 @@ TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* wor
   if (vocab < 1) return TS_ERR_SIZE;
   if (work == nullptr || tokens == nullptr) return TS_ERR_ARGUMENT;
   ts_launch(sample_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
-                                                         temperature, top_k, top_p, penalty, seed,
-                                                         counter, history, history_start, tokens,
-                                                         logprobs);
+            temperature, top_k, top_p, penalty, seed, counter, history, history_start, tokens, logprobs,
+            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr);
+  return ts_launch_status();
+}
+
+// Words of `partial` that ts_sample_slots needs for (rows, chunks).
+TS_EXPORT long long ts_sample_partial_words(int num_rows, int chunks) {
+  return (long long)num_rows * (2 * (long long)chunks + 1);
+}
+
+// The same with the options looked up by state slot (see the head of this file): temperature,
+// top_k, top_p, seed and prompt_len are arrays over the slots, row_slot / row_seq / row_context
+// are per row, `partial` is zeroed scratch of ts_sample_partial_words(num_rows, chunks) words
+// that the kernel leaves zeroed where it matters, chunks >= 1.  No penalty, no log-probabilities.
+TS_EXPORT int ts_sample_slots(const float* logits, long long logits_stride, float* work, int num_rows,
+                              int vocab, const float* temperature, const int* top_k, const float* top_p,
+                              const unsigned long long* seed, const int* prompt_len, const int* row_slot,
+                              const int* row_seq, const int* row_context, int* tokens, int* partial,
+                              int chunks, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (vocab < 1 || chunks < 1 || chunks > 64) return TS_ERR_SIZE;
+  if (work == nullptr || tokens == nullptr || row_slot == nullptr || row_context == nullptr || prompt_len == nullptr ||
+      temperature == nullptr || partial == nullptr)
+    return TS_ERR_ARGUMENT;
+  ts_launch(sample_kernel, dim3(num_rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
+            temperature, top_k, top_p, (const float*)nullptr, seed, (const unsigned int*)nullptr, (const int*)nullptr,
+            (const int*)nullptr, tokens, (float*)nullptr, row_slot, row_seq, row_context, prompt_len, partial);
   return ts_launch_status();
 }
 

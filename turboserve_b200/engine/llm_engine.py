@@ -70,7 +70,11 @@ class LLMEngine:
         self.cache = cache
         self.scheduler = scheduler if scheduler is not None else Scheduler(config.scheduler, cache)
         self.scheduler.copy_tables = False  # a step runs before anything else can touch the tables
-        self.sampler = sampler if sampler is not None else Sampler(runner.device)
+        if sampler is None:
+            # a runner whose captured graphs already end with a sampler keeps that sampler: its options by
+            # state slot are what those graphs read
+            sampler = getattr(runner, "graph_sampler", None) or Sampler(runner.device)
+        self.sampler = sampler
         self._eos_token_ids = frozenset(int(t) for t in getattr(self.model.spec, "eos_token_ids", ()))
         self._seed_source = random.Random(config.seed)
         self._num_generated_tokens = 0
@@ -81,6 +85,13 @@ class LLMEngine:
         self._in_flight: _Flight | None = None
         self._num_overlapped_steps = 0
         if config.cuda_graphs and self.runner.dtype == torch.bfloat16 and hasattr(self.runner, "enable_graphs"):
+            captured_with = getattr(self.runner, "graph_sampler", None)
+            if hasattr(self.sampler, "use_slots") and (captured_with is self.sampler or not self.runner._graphs):
+                # options by state slot on the device: a captured decode step samples its own tokens
+                self.sampler.use_slots(config.scheduler.max_num_seqs, self.model.vocab_size)
+                self.runner.graph_sampler = self.sampler
+            elif captured_with is not None:
+                self.runner.graph_sampler = None  # graphs captured with another sampler: their ids are not used
             pages = min(g.num_pages for g in self.runner.groups)
             longest = min(config.max_model_len or pages * config.block_size, pages * config.block_size)
             self.runner.enable_graphs(config.scheduler.max_num_seqs, longest, config.scheduler.max_num_batched_tokens)
@@ -154,7 +165,10 @@ class LLMEngine:
             outputs = [seq.to_output(full=True) for seq in plan.dropped]
             for seq in plan.admitted:
                 if seq.request_id in self.cache:
-                    self.runner.reset_state_slot(self.cache.state_slot(seq.request_id))
+                    slot = self.cache.state_slot(seq.request_id)
+                    self.runner.reset_state_slot(slot)
+                    if getattr(self.sampler, "slots", None) is not None:
+                        self.sampler.slots.set(slot, seq.sampling, seq.seed, seq.num_prompt_tokens)
             if plan.is_empty:
                 return outputs
             flight = self._launch(plan, ahead=False)
@@ -202,10 +216,16 @@ class LLMEngine:
     def _launch(self, plan: SchedulerOutput, ahead: bool) -> "_Flight":
         """Run and sample ``plan``; the ids stay on the device until :meth:`_Flight.result`."""
         pending = 1 if ahead else 0  # tokens of a request that are sampled but not read yet: they count for the draw's index
+        if getattr(self.sampler, "slots", None) is not None:
+            self.sampler.slots.flush()
         logits = self.runner.step(plan.slices(), device_tokens=self.runner.token_buffer if ahead else None)
         seqs = plan.sampling_seqs()
         if not seqs:
             return _Flight(plan, None, None, None)
+        if getattr(self.runner, "sampled_in_graph", False) and all(self.sampler.fits_slots(s.sampling) for s in seqs):
+            # the replayed graph ended with the sampler, options by state slot: the ids are in token_buffer
+            rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending) for s in seqs]
+            return _Flight(plan, rows, self.runner.start_token_read(len(rows)), None)
         rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending,
                             s.token_ids if s.sampling.repetition_penalty != 1.0 else ()) for s in seqs]
         tokens, logprobs = self.sampler.sample_device(logits, rows, out=self.runner.token_buffer[:-1])

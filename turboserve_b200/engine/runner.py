@@ -93,6 +93,11 @@ class ModelRunner:
         self.num_steps = 0
         self.num_graph_replays = 0
         self.num_graph_captures = 0
+        self.graph_sampler = None
+        """A sampler with per-slot options (``Sampler.use_slots``): captured decode graphs then end with
+        its kernel, which leaves the step's token ids in :attr:`token_buffer` (:attr:`sampled_in_graph`)."""
+        self.sampled_in_graph = False
+        """Whether the step that ran last was a graph replay that sampled its own tokens."""
         self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, StaticBatch, torch.Tensor]] = {}
         self._graph_buckets: list[int] = []
         self._graph_widths: list[int] = []
@@ -129,6 +134,7 @@ class ModelRunner:
                         raise ValueError(f"token id {token} is outside the vocabulary of {vocab}")
         if self._graph_buckets and self._is_plain_decode(slices):
             return self._replay_decode(slices, device_tokens)
+        self.sampled_in_graph = False
         batch = self.build_batch(slices)
         if device_tokens is not None:
             batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
@@ -208,6 +214,10 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = self.run(static.batch)
+            if self.graph_sampler is not None:
+                batch = static.batch
+                self.graph_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
+                                                  bucket, self.token_buffer[:-1])
         entry = (graph, static, logits)
         self._graphs[(bucket, skew)] = entry
         self.num_graph_captures += 1
@@ -244,6 +254,7 @@ class ModelRunner:
         graph.replay()
         self.num_steps += 1
         self.num_graph_replays += 1
+        self.sampled_in_graph = self.graph_sampler is not None
         return logits[: len(slices)]
 
     def start_token_read(self, count: int) -> "TokenRead":

@@ -271,6 +271,33 @@ def sample(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor, *, nu
               _ptr(logprobs), _stream()), "sample")
 
 
+def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor, num_rows: int, *, temperature: torch.Tensor,
+                 top_k: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor, prompt_len: torch.Tensor,
+                 row_slot: torch.Tensor, row_seq: torch.Tensor | None, row_context: torch.Tensor, partial: torch.Tensor,
+                 chunks: int) -> None:
+    """One token per row with the options looked up by state slot (arrays over the slots); the index of
+    the token being generated is ``row_context[row] - prompt_len[slot]``. A row with ``row_seq < 0`` is
+    skipped. ``partial`` is zeroed int32 scratch of ``rows * (2 * chunks + 1)`` words; a row that needs
+    one pass only (greedy, or a draw without top-k and top-p) is cut into ``chunks`` blocks."""
+    _need(logits, torch.float32, "logits"); _need(work, torch.float32, "work"); _need(tokens, torch.int32, "tokens")
+    vocab = logits.shape[1]
+    if work.numel() < num_rows * vocab or not work.is_contiguous():
+        raise KernelError("sample_slots: work must hold rows * vocab floats")
+    for name, tensor, dtype in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                                ("top_p", top_p, torch.float32), ("seed", seed, torch.int64), ("prompt_len", prompt_len, torch.int32),
+                                ("row_slot", row_slot, torch.int32), ("row_context", row_context, torch.int32),
+                                ("partial", partial, torch.int32)):
+        _need(tensor, dtype, name)
+    if row_seq is not None:
+        _need(row_seq, torch.int32, "row_seq")
+    if partial.numel() < num_rows * (2 * chunks + 1):
+        raise KernelError("sample_slots: partial is too small")
+    fn = _fn("sampling", "ts_sample_slots", [c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 10 + [c_int, c_void_p])
+    _check(fn(_ptr(logits), logits.stride(0), _ptr(work), num_rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+              _ptr(seed), _ptr(prompt_len), _ptr(row_slot), _ptr(row_seq), _ptr(row_context), _ptr(tokens), _ptr(partial),
+              int(chunks), _stream()), "sample_slots")
+
+
 def sample_uniform_host(seed: int, counter: int, index: int) -> float:
     fn = _fn("sampling", "ts_sample_uniform_host", [ctypes.c_ulonglong, ctypes.c_uint, ctypes.c_uint], restype=c_float)
     return float(fn(seed & 0xFFFFFFFFFFFFFFFF, counter, index))

@@ -8,6 +8,13 @@ counter-based uniforms of (request seed, index of the generated token, vocabular
 request's tokens do not depend on its batch neighbours, on how often it was preempted, or on
 any global generator. All of it is one kernel (``sampling.cu``); a batch of plain greedy rows
 takes the argmax kernel, which needs no scratch.
+
+Per-request options also live on the device, by state slot (:class:`SlotOptions`): they are
+written once, when a request is admitted, and a decode step finds them through the step's
+``state_slots``; the index of the token being generated follows from the request's length, so
+nothing has to be sent or advanced per step and the sampler is part of a captured decode graph
+(:meth:`Sampler.sample_by_slot`). Rows that want a repetition penalty or log-probabilities
+still go the other way, with their options sent along.
 """
 
 from __future__ import annotations
@@ -37,10 +44,87 @@ class SamplingRow:
     history: SequenceABC[int] = ()
 
 
+SLOT_CHUNKS = 8
+"""Blocks a row is cut into when one pass over it is enough (greedy, or a draw without top-k and top-p)."""
+
+
+class SlotOptions:
+    """Sampling options of the live requests on the device, one entry per state slot.
+
+    ``temperature``, ``top_p`` (float32), ``top_k``, ``prompt_len`` (int32) and ``seed`` (int64) are
+    arrays over the slots. A host mirror in pinned memory is changed at admission and copied
+    over whole (a few hundred bytes, on the stream, so in order with the steps around it).
+    """
+
+    def __init__(self, num_slots: int, device: torch.device) -> None:
+        self.num_slots = int(num_slots)
+        pin = device.type == "cuda"
+        self._host_f = torch.zeros(2 * num_slots, dtype=torch.float32)
+        self._host_i = torch.zeros(2 * num_slots, dtype=torch.int32)
+        self._host_s = torch.zeros(num_slots, dtype=torch.int64)
+        if pin:
+            self._host_f, self._host_i, self._host_s = self._host_f.pin_memory(), self._host_i.pin_memory(), self._host_s.pin_memory()
+        self._host_f[num_slots:] = 1.0  # top_p
+        self._dev_f = self._host_f.to(device)
+        self._dev_i = self._host_i.to(device)
+        self.seed = self._host_s.to(device)
+        self.temperature, self.top_p = self._dev_f[:num_slots], self._dev_f[num_slots:]
+        self.top_k, self.prompt_len = self._dev_i[:num_slots], self._dev_i[num_slots:]
+        self._dirty = False
+
+    def set(self, slot: int, params: SamplingParams, seed: int, num_prompt_tokens: int) -> None:
+        n = self.num_slots
+        # a request that needs its history or a log-probability is sampled with its options sent along;
+        # a negative temperature tells the kernel that reads these arrays to leave its row alone
+        self._host_f[slot] = params.temperature if Sampler.fits_slots(params) else -1.0
+        self._host_f[n + slot] = params.top_p
+        self._host_i[slot] = params.top_k
+        self._host_i[n + slot] = num_prompt_tokens
+        self._host_s[slot] = seed & 0x7FFFFFFFFFFFFFFF
+        self._dirty = True
+
+    def flush(self) -> None:
+        """Bring the device arrays up to date (before the step that first uses what was set)."""
+        if self._dirty:
+            self._dev_f.copy_(self._host_f, non_blocking=True)
+            self._dev_i.copy_(self._host_i, non_blocking=True)
+            self.seed.copy_(self._host_s, non_blocking=True)
+            self._dirty = False
+
+
 class Sampler:
     def __init__(self, device: torch.device | str) -> None:
         self.device = torch.device(device)
         self._work: torch.Tensor | None = None
+        self.slots: SlotOptions | None = None
+        self._partial: torch.Tensor | None = None
+
+    def use_slots(self, num_slots: int, vocab: int) -> SlotOptions:
+        """Keep per-request options on the device for up to ``num_slots`` requests; sizes the scratch
+        of :meth:`sample_by_slot` once, so that it can be part of a captured graph."""
+        if self.slots is None or self.slots.num_slots < num_slots:
+            self.slots = SlotOptions(num_slots, self.device)
+            self._partial = torch.zeros(num_slots * (2 * SLOT_CHUNKS + 1), dtype=torch.int32, device=self.device)
+        self._scratch(num_slots, vocab)
+        return self.slots
+
+    @staticmethod
+    def fits_slots(params: SamplingParams) -> bool:
+        """Whether a row with these options can be sampled from the slot arrays (no penalty, no log-probabilities)."""
+        return params.repetition_penalty == 1.0 and not params.logprobs
+
+    def sample_by_slot(self, logits: torch.Tensor, row_slot: torch.Tensor, row_seq: torch.Tensor | None,
+                       row_context: torch.Tensor, num_rows: int, out: torch.Tensor) -> torch.Tensor:
+        """Sample ``num_rows`` rows whose options are in :attr:`slots`; ids into ``out``. Allocates nothing."""
+        if self.slots is None or self._partial is None:
+            raise RuntimeError("use_slots() first")
+        slots = self.slots
+        kernels.sample_slots(
+            logits, self._scratch(num_rows, logits.shape[1]), out, num_rows, temperature=slots.temperature, top_k=slots.top_k,
+            top_p=slots.top_p, seed=slots.seed, prompt_len=slots.prompt_len, row_slot=row_slot, row_seq=row_seq,
+            row_context=row_context, partial=self._partial, chunks=SLOT_CHUNKS,
+        )
+        return out[:num_rows]
 
     def _scratch(self, rows: int, vocab: int) -> torch.Tensor:
         need = rows * vocab
