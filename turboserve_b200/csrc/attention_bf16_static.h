@@ -30,6 +30,10 @@
  * It calls no cudaMalloc, cudaFree or any routine that allocates.  The first call on a device
  * (with that device current) looks up the array's device address with cudaGetSymbolAddress and
  * remembers it; make that first call during start-up, before any stream capture begins.
+ * The CUDA runtime itself may load a kernel's code the first time that kernel is launched (lazy
+ * module loading), which can take device memory outside this library's control: a caller for
+ * whom that matters warms up each head size it will use with one call with num_splits > 1 at
+ * start-up (that launches both kernels), or runs with CUDA_MODULE_LOADING=EAGER.
  *
  * All calls on a device share the one array and the array keeps what the last call left in it.
  * Nothing in it has to be cleared between calls: every slot the joining kernel reads is written

@@ -88,7 +88,9 @@ class LLMEngine:
             captured_with = getattr(self.runner, "graph_sampler", None)
             if hasattr(self.sampler, "use_slots") and (captured_with is self.sampler or not self.runner._graphs):
                 # options by state slot on the device: a captured decode step samples its own tokens
-                self.sampler.use_slots(config.scheduler.max_num_seqs, self.model.vocab_size)
+                # as many slots as the runner has (it may have been built for more requests than this engine admits)
+                self.sampler.use_slots(max(config.scheduler.max_num_seqs, self.runner.token_buffer.numel() - 1),
+                                       self.model.vocab_size)
                 self.runner.graph_sampler = self.sampler
             elif captured_with is not None:
                 self.runner.graph_sampler = None  # graphs captured with another sampler: their ids are not used
