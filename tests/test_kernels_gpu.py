@@ -438,7 +438,7 @@ def test_flash_kernels_find_one_far_key_and_respect_the_window_edge(decode):
     (28, 4, 128, 16, None, [300, 280, 310, 290]),                        # an even batch: as before
     (28, 4, 128, 16, None, [300] * 40 + [5000]),                         # many requests: 1 part each when even, 8 here
 ])
-def test_a_lopsided_decode_batch_cuts_every_request_into_more_parts(nh, nkv, d, page, window, contexts):
+def test_a_lopsided_decode_batch_is_cut_by_each_requests_own_length(nh, nkv, d, page, window, contexts):
     from turboserve_b200.engine.batch import RequestSlice, StepContext, Workspace, build_step_batch, skew_class
     from turboserve_b200.ops import kernels
     from turboserve_b200.ops.skinny import num_sms
@@ -457,10 +457,21 @@ def test_a_lopsided_decode_batch_cuts_every_request_into_more_parts(nh, nkv, d, 
     launched = kernels.launch_count() - before
     sms, n = num_sms(torch.device(DEV)), len(contexts)
     even = fa.decode_splits(n, nkv, sms)
-    parts = min(even * batch.decode_skew, fa.MAX_SPLITS, (n + fa.SKEW_SPLIT_ROOM * ((2 * sms) // nkv)) // n)
-    if batch.decode_skew > 1:
-        assert parts > even or even == fa.MAX_SPLITS
-    assert launched == (2 if parts > fa.CLUSTER_MAX_SPLITS else 1)  # more parts than a cluster holds: the join kernel follows
+    if batch.decode_skew >= fa.WORK_LIST_FROM and fa.tma_decode_supports(d, page, nh // nkv):
+        # the kernel that walks a work list: every request cut by its own length, joined by the second kernel
+        assert launched == 2
+        items = batch.decode_items[int(window or 0)]
+        parts_of = items.parts_of[:n].tolist()
+        visible = [min(c, window) if window else c for c in contexts]
+        assert parts_of[visible.index(max(visible))] == max(parts_of)
+        if max(visible) > 1024:
+            assert max(parts_of) > min(parts_of)
+        assert items.num_items == sum(parts_of) <= n + fa.decode_item_target(nkv, sms)
+    else:
+        parts = min(even * batch.decode_skew, fa.MAX_SPLITS, (n + fa.SKEW_SPLIT_ROOM * ((2 * sms) // nkv)) // n)
+        if batch.decode_skew > 1:
+            assert parts > even or even == fa.MAX_SPLITS
+        assert launched == (2 if parts > fa.CLUSTER_MAX_SPLITS else 1)  # more parts than a cluster holds: the join kernel follows
     assert status.item() == 0
     got = out.view(len(contexts), nh, d).double().cpu()
     assert torch.isfinite(got).all()
@@ -889,3 +900,38 @@ def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row
         t, k, p, s, plen = slot_opts[row_slot[r]]
         expect, _ = P.sample_token(logits[r].cpu(), temperature=t, top_k=k, top_p=p, seed=s, counter=row_context[r] - plen)
         assert tokens[r].item() == expect
+
+
+@pytest.mark.parametrize("nh, nkv, page, window", [(28, 4, 16, None), (5, 1, 8, 300), (16, 2, 64, None)])
+def test_decode_attention_over_a_work_list(nh, nkv, page, window):
+    """Every request cut into parts by its own length: more parts than a short request has 64-key tiles
+    (some are empty), one part (the output is written at once, the join kernel skips it), unused
+    items and a padding token at the end of the list."""
+    from turboserve_b200.engine.batch import DecodeItems, plan_decode_items
+    from turboserve_b200.ops import attention_bf16 as fa
+
+    d = 128
+    contexts = [5000, 1, 70, 640, 129, 64]
+    q_lens = [1] * len(contexts)
+    _, q, k_pages, v_pages, table, positions, seq_of, ref, scale = flash_case(nh, nkv, d, page, window, contexts, q_lens, seed=61)
+    live, n = len(contexts), len(contexts) + 1
+    visible = [min(c, window) if window else c for c in contexts]
+    item_token, item_part, parts_of, first_item = plan_decode_items(visible, target_items=40, min_keys=64)
+    parts_of[2], first_item = 3, None  # a 70-key request in three parts: its third part has no tile
+    first_item = [sum(parts_of[:i]) for i in range(live)]
+    pairs = [(i, p) for i in sorted(range(live), key=lambda r: -visible[r]) for p in range(parts_of[i])]
+    item_token, item_part = [t for t, _ in pairs] + [-1, -1], [p for _, p in pairs] + [0, 0]
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    items = DecodeItems(dev(item_token), dev(item_part), dev(parts_of + [1]), dev(first_item + [0]), len(item_token))
+    assert max(parts_of) > 3 and min(parts_of) == 1
+    qp = torch.cat([q, torch.zeros(1, nh * d, dtype=torch.bfloat16, device=DEV)])
+    pad = lambda t, fill: torch.cat([t, torch.full((1,), fill, dtype=t.dtype, device=DEV)])
+    out = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scratch = torch.full((items.num_items * nh * (d + 2),), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fa.flash_decode_tma_items(qp, out, k_pages, v_pages, table, pad(seq_of, -1), pad(positions, 0), n, nh, nkv, d, window, scale,
+                              items, scratch, status)
+    assert status.item() == 0
+    got = out[:live].view(live, nh, d).double().cpu()
+    assert torch.isfinite(got).all() and torch.isnan(out[live:].float()).all()
+    assert (got - ref).abs().max().item() < 2e-2, (got - ref).abs().max().item()

@@ -401,8 +401,15 @@ __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2
                                               bool active, int warp, int lane, int group, int kv_head, int token,
                                               int split, int num_splits, int num_heads, bf16* __restrict__ out,
                                               long long out_stride, float* __restrict__ partial_o,
-                                              float* __restrict__ partial_ml) {
+                                              float* __restrict__ partial_ml, long long slot0 = -1,
+                                              long long slot_stride = 0) {
   const int g = lane >> 2, t = lane & 3;
+  // where this block's partial result of head h goes in scratch: slot0 + h * slot_stride; by
+  // default the layout [tokens, heads, splits]
+  if (slot0 < 0) {
+    slot0 = (long long)token * num_heads * num_splits + split;
+    slot_stride = num_splits;
+  }
   // each warp writes (m, l) per row and its O tile; then all read them
   float* join_o = decode_join_o<D>(smem_raw);                    // [SLOTS][16][D]
   float* join_ml = decode_join_ml<D, SLOTS>(smem_raw);           // [SLOTS][16][2]
@@ -455,7 +462,7 @@ __device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2
       *reinterpret_cast<unsigned*>(dst) = pack_bf16(acc[0] * inv, acc[1] * inv);
       *reinterpret_cast<unsigned*>(dst + 2) = pack_bf16(acc[2] * inv, acc[3] * inv);
     } else {
-      const size_t slot = ((size_t)token * num_heads + head) * num_splits + split;
+      const size_t slot = (size_t)(slot0 + (long long)head * slot_stride);
       float* dst = partial_o + slot * D + d0;
       *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       if (d0 == 0) {
@@ -741,6 +748,17 @@ __device__ __forceinline__ unsigned dtma_offset(int r, int c) {
   return (unsigned)((c >> 3) * DTMA_HALF + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+// A work list for decode steps whose requests differ much in length: item i is part
+// item_part[i] of token item_token[i] (-1: unused); token t is cut into parts_of[t] parts, whose
+// items lie one after the other from first_item[t].  All null: no list, every token is cut into
+// the same number of parts by the grid.
+struct DecodeItems {
+  const int* item_token;
+  const int* item_part;
+  const int* parts_of;
+  const int* first_item;
+};
+
 // What the kernel needs to do the step before attention itself (FUSED): the raw q/k/v product of
 // the step's tokens, the bias, the rotation's constants, and the pages to append to.  The block
 // of a (request, kv head) adds the bias to its query heads and rotates them (fp32, rounded to
@@ -777,7 +795,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                         int page_shift, int box_rows, int total_rows, int num_heads, int num_kv_heads,
                         int window, float scale_log2, int num_splits, float* __restrict__ partial_o,
-                        float* __restrict__ partial_ml, int* __restrict__ status, const DecodeFusion fusion) {
+                        float* __restrict__ partial_ml, int* __restrict__ status, const DecodeFusion fusion,
+                        const DecodeItems items) {
   constexpr int D = 128;
   constexpr int SLOTS = FUSED ? FLASH_WARPS + 1 : FLASH_WARPS;
   if (!FUSED) pdl_wait();  // no early trigger: with it the decode step was 0.2 ms slower (3.42 against 3.21 ms)
@@ -789,7 +808,23 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   __shared__ __align__(16) bf16 kv_s[FUSED ? 2 * D : 8];               // the token's own key (rotated), then value
   __shared__ float cs_s[FUSED ? D : 2];                                 // cos, then sin, of the token's angles
 
-  const int split = blockIdx.x, kv_head = blockIdx.y, token = blockIdx.z;
+  // Which part of which token this block works on: by its place in the grid (every token cut
+  // into num_splits parts), or, with a work list, by item blockIdx.x of the list, whose tokens are
+  // cut into as many parts as their own length asks for (items.parts_of) and leave their partial
+  // results at [items.first_item[token] + part][head] of the scratch.
+  int split = blockIdx.x, token = blockIdx.z;
+  const int kv_head = blockIdx.y;
+  long long slot0 = -1;
+  if (items.item_token != nullptr) {
+    token = items.item_token[blockIdx.x];
+    if (token < 0) {  // an unused item
+      if (FUSED) pdl_wait();
+      return;
+    }
+    split = items.item_part[blockIdx.x];
+    num_splits = items.parts_of[token];
+    slot0 = (long long)(items.first_item[token] + split) * num_heads;
+  }
   const int seq = seq_of_token[token];
   if (seq < 0) {  // the same for every block of a cluster: nothing has been set up
     if (FUSED) pdl_wait();
@@ -811,7 +846,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // join, and nothing else to do (the same for every thread; nothing has been set up)
     if (FUSED) pdl_wait();
     if ((int)threadIdx.x < group) {
-      const size_t slot = ((size_t)token * num_heads + kv_head * group + threadIdx.x) * num_splits + split;
+      const int head = kv_head * group + threadIdx.x;
+      const size_t slot = slot0 >= 0 ? (size_t)(slot0 + head) : ((size_t)token * num_heads + head) * num_splits + split;
       partial_ml[slot * 2] = -INFINITY;
       partial_ml[slot * 2 + 1] = 0.0f;
     }
@@ -1077,7 +1113,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
   }
   decode_finish<D, CLUSTER, SLOTS>(o, m, l, ring_ptr, warp < FLASH_WARPS, warp, lane, group, kv_head, token, split,
-                                   num_splits, num_heads, out, out_stride, partial_o, partial_ml);
+                                   num_splits, num_heads, out, out_stride, partial_o, partial_ml, slot0, 1);
 }
 
 // Join the splits of a decode step: one block per (token, head), one thread per dim.
@@ -1085,21 +1121,30 @@ template <int D>
 __global__ void __launch_bounds__(D)
 flash_decode_join_kernel(bf16* __restrict__ out, long long out_stride,
                          const int* __restrict__ seq_of_token, int num_heads, int num_splits,
-                         const float* __restrict__ partial_o, const float* __restrict__ partial_ml) {
+                         const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                         const int* __restrict__ parts_of, const int* __restrict__ first_item) {
   pdl_wait();
   pdl_trigger<8>();
   const int head = blockIdx.x, token = blockIdx.y;
   if (seq_of_token[token] < 0) return;
-  const size_t slot0 = ((size_t)token * num_heads + head) * num_splits;
+  // part s of this (token, head) is at slot0 + s * stride: [tokens, heads, splits], or with a work
+  // list [items, heads] with the token's items one after the other
+  size_t slot0 = ((size_t)token * num_heads + head) * num_splits, stride = 1;
+  if (parts_of != nullptr) {
+    num_splits = parts_of[token];
+    if (num_splits == 1) return;  // the one part wrote the output row itself
+    slot0 = (size_t)first_item[token] * num_heads + head;
+    stride = num_heads;
+  }
   float m_all = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, partial_ml[(slot0 + s) * 2]);
+  for (int s = 0; s < num_splits; ++s) m_all = fmaxf(m_all, partial_ml[(slot0 + s * stride) * 2]);
   float l_all = 0.0f, acc = 0.0f;
   for (int s = 0; s < num_splits; ++s) {
-    const float ms = partial_ml[(slot0 + s) * 2];
+    const float ms = partial_ml[(slot0 + s * stride) * 2];
     const float w = ms == -INFINITY ? 0.0f : exp2f(ms - m_all);
     if (w > 0.0f) {  // a part without keys leaves no rows behind, only its (-inf, 0)
-      l_all += partial_ml[(slot0 + s) * 2 + 1] * w;
-      acc += partial_o[(slot0 + s) * D + threadIdx.x] * w;
+      l_all += partial_ml[(slot0 + s * stride) * 2 + 1] * w;
+      acc += partial_o[(slot0 + s * stride) * D + threadIdx.x] * w;
     }
   }
   out[(size_t)token * out_stride + (size_t)head * D + threadIdx.x] =
@@ -1191,7 +1236,7 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, long long
   if (code || num_splits == 1) return code;
   dim3 join_grid(num_heads, num_tokens);
   ts_launch(flash_decode_join_kernel<D>, dim3(join_grid), dim3(D), 0, stream, out, out_stride, seq_of_token, num_heads,
-                                                            num_splits, partial_o, partial_ml);
+            num_splits, (const float*)partial_o, (const float*)partial_ml, (const int*)nullptr, (const int*)nullptr);
   return ts_launch_status();
 }
 
@@ -1277,7 +1322,7 @@ static int flash_decode_tma_checked(const void* q, long long q_stride, void* out
                                     const int* positions, int num_tokens, int page_size, int num_heads,
                                     int num_kv_heads, int head_dim, int window, float scale, int num_splits,
                                     float* scratch, int* status, const DecodeFusion& fusion, bool allow_cluster,
-                                    cudaStream_t stream) {
+                                    const DecodeItems& items, int num_items, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int bad = check_common(q, q_stride, out, out_stride, head_dim, num_heads, num_kv_heads, page_size);
   if (bad) return bad;
@@ -1286,8 +1331,11 @@ static int flash_decode_tma_checked(const void* q, long long q_stride, void* out
   if (((uintptr_t)q & 3) || (q_stride & 1)) return TS_ERR_ALIGN;
   if (((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return TS_ERR_ALIGN;
   if (num_splits < 1 || num_splits > 65535 || num_kv_heads > 65535 || num_tokens > 65535) return TS_ERR_SIZE;
-  const bool cluster = allow_cluster && num_splits >= 2 && num_splits <= DECODE_CLUSTER_MAX;
-  if (num_splits > 1 && !cluster && (scratch == nullptr || ((uintptr_t)scratch & 15))) return TS_ERR_ARGUMENT;
+  const bool listed = items.item_token != nullptr;
+  if (listed && (num_items < 1 || num_items > 65535 || !items.item_part || !items.parts_of || !items.first_item))
+    return TS_ERR_ARGUMENT;
+  const bool cluster = !listed && allow_cluster && num_splits >= 2 && num_splits <= DECODE_CLUSTER_MAX;
+  if ((num_splits > 1 || listed) && !cluster && (scratch == nullptr || ((uintptr_t)scratch & 15))) return TS_ERR_ARGUMENT;
   const long long rows = num_pages * page_size;
   if (rows <= 0 || rows >= (1ll << 31) - 256) return TS_ERR_SIZE;
   const int box_rows = page_size < DTMA_KEYS ? page_size : DTMA_KEYS;
@@ -1299,25 +1347,28 @@ static int flash_decode_tma_checked(const void* q, long long q_stride, void* out
   const float scale_log2 = scale * 1.4426950408889634f;
   const int shift = page_shift_of(page_size);
   float* partial_o = scratch;
-  float* partial_ml = scratch ? scratch + (size_t)num_tokens * num_heads * num_splits * head_dim : nullptr;
-  const dim3 grid(num_splits, num_kv_heads, num_tokens);
+  // scratch: the partial rows of every slot, then their (max, sum): [tokens, heads, splits], or [items, heads]
+  const size_t slots = listed ? (size_t)num_items * num_heads : (size_t)num_tokens * num_heads * num_splits;
+  float* partial_ml = scratch ? scratch + slots * head_dim : nullptr;
+  const dim3 grid = listed ? dim3(num_items, num_kv_heads, 1) : dim3(num_splits, num_kv_heads, num_tokens);
   if (cluster) {
     cudaFuncSetAttribute(flash_decode_tma_kernel<true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
     ts_launch_cluster(flash_decode_tma_kernel<true, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, num_splits, map_k,
                       map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token,
                       positions, shift, box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                      (float*)nullptr, (float*)nullptr, status, fusion);
+                      (float*)nullptr, (float*)nullptr, status, fusion, items);
     return ts_launch_status();
   }
   cudaFuncSetAttribute(flash_decode_tma_kernel<false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
   ts_launch(flash_decode_tma_kernel<false, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, map_k, map_v,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token, positions, shift,
             box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
-            fusion);
+            fusion, items);
   code = ts_launch_status();
-  if (code || num_splits == 1) return code;
+  if (code || (num_splits == 1 && !listed)) return code;
   ts_launch(flash_decode_join_kernel<128>, dim3(num_heads, num_tokens), dim3(128), 0, stream, (bf16*)out, out_stride,
-            seq_of_token, num_heads, num_splits, partial_o, partial_ml);
+            seq_of_token, num_heads, num_splits, (const float*)partial_o, (const float*)partial_ml, items.parts_of,
+            items.first_item);
   return ts_launch_status();
 }
 
@@ -1331,7 +1382,28 @@ TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, 
   memset(&none, 0, sizeof(none));
   return flash_decode_tma_checked<false>(q, q_stride, out, out_stride, k_pages, v_pages, num_pages, block_table,
                                          table_stride, seq_of_token, positions, num_tokens, page_size, num_heads,
-                                         num_kv_heads, head_dim, window, scale, num_splits, scratch, status, none, true, stream);
+                                         num_kv_heads, head_dim, window, scale, num_splits, scratch, status, none, true,
+                                         DecodeItems{nullptr, nullptr, nullptr, nullptr}, 0, stream);
+}
+
+// The same with a work list instead of one number of parts for every token (see DecodeItems):
+// item_token / item_part hold num_items items (the grid), parts_of / first_item one entry per
+// token; scratch holds num_items * num_heads * (head_dim + 2) floats.  A token with one part
+// writes its output row itself, the others are joined by the second kernel.
+TS_EXPORT int ts_flash_decode_tma_items(const void* q, long long q_stride, void* out, long long out_stride,
+                                        const void* k_pages, const void* v_pages, long long num_pages,
+                                        const int* block_table, int table_stride, const int* seq_of_token,
+                                        const int* positions, int num_tokens, int page_size, int num_heads,
+                                        int num_kv_heads, int head_dim, int window, float scale,
+                                        const int* item_token, const int* item_part, const int* parts_of,
+                                        const int* first_item, int num_items, float* scratch, int* status,
+                                        cudaStream_t stream) {
+  DecodeFusion none;
+  memset(&none, 0, sizeof(none));
+  return flash_decode_tma_checked<false>(q, q_stride, out, out_stride, k_pages, v_pages, num_pages, block_table,
+                                         table_stride, seq_of_token, positions, num_tokens, page_size, num_heads,
+                                         num_kv_heads, head_dim, window, scale, 1, scratch, status, none, false,
+                                         DecodeItems{item_token, item_part, parts_of, first_item}, num_items, stream);
 }
 
 // The same, with the step before attention done by the kernel itself (see DecodeFusion): qkv is
@@ -1362,7 +1434,7 @@ TS_EXPORT int ts_flash_decode_tma_fused(const void* qkv, long long qkv_stride, c
   return flash_decode_tma_checked<true>(qkv, qkv_stride, out, out_stride, k_pages, v_pages, num_pages, block_table,
                                         table_stride, seq_of_token, positions, num_tokens, page_size, num_heads,
                                         num_kv_heads, head_dim, window, scale, num_splits, scratch, status, fusion,
-                                        allow_cluster != 0, stream);
+                                        allow_cluster != 0, DecodeItems{nullptr, nullptr, nullptr, nullptr}, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

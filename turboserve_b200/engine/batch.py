@@ -55,7 +55,12 @@ class StepBatch:
     max_context_len: int = 0
     decode_skew: int = 1
     """1, 2, 4, 8 or 16: how far the longest context of the requests that decode lies above their mean
-    (:func:`skew_class`); the attention kernels cut every request's keys into that many times more parts."""
+    (:func:`skew_class`). At 2 decode attention cuts every request's keys into twice the parts; from 4
+    on it cuts every request into parts by its own length (a work list, :func:`plan_decode_items`), or,
+    in kernels that take no list, every request's keys into that many times more parts."""
+
+    decode_items: dict[int, "DecodeItems"] = field(default_factory=dict)
+    """Work lists of a lopsided decode step that were made with the batch, by the window they are for (0: none)."""
 
     @property
     def is_decode_only(self) -> bool:
@@ -101,6 +106,52 @@ def skew_class(contexts: Sequence[int]) -> int:
         if ratio >= cls:
             return cls
     return 1
+
+
+WORK_LIST_FROM = 4
+"""The class of lopsidedness from which a decode step brings a work list (the attention kernels' rule, ``ops/attention_bf16.py``)."""
+DECODE_ITEM_KEYS = 256
+"""The fewest keys a part of a request is worth a block for."""
+DECODE_ITEM_MAX_PARTS = 64
+
+
+def plan_decode_items(visible: Sequence[int], target_items: int, min_keys: int = DECODE_ITEM_KEYS,
+                      max_parts: int = DECODE_ITEM_MAX_PARTS, tile: int = 64):
+    """Cut the requests of a decode step into parts of about equal length: the work list of decode attention.
+
+    ``visible[i]`` is the number of keys request ``i`` attends to. All keys together are cut into
+    about ``target_items`` parts of one length (a multiple of ``tile``, at least ``min_keys``);
+    a request gets as many parts as its own keys fill, at least one and at most ``max_parts``.
+    Returns ``(item_token, item_part, parts_of, first_item)`` as lists: item ``k`` is part
+    ``item_part[k]`` of request ``item_token[k]``, the longest requests' items first (their blocks
+    start first); request ``i`` has ``parts_of[i]`` parts whose partial results lie in scratch from
+    slot ``first_item[i]`` on. There are never more than ``len(visible) + target_items`` items.
+    """
+    n = len(visible)
+    total = sum(max(0, int(v)) for v in visible)
+    length = max(min_keys, -(-total // max(1, target_items)))
+    length = -(-length // tile) * tile
+    parts_of = [min(max_parts, max(1, -(-max(0, int(v)) // length))) for v in visible]
+    first_item, cursor = [0] * n, 0
+    for i in range(n):
+        first_item[i] = cursor
+        cursor += parts_of[i]
+    item_token, item_part = [], []
+    for i in sorted(range(n), key=lambda r: -visible[r]):
+        item_token += [i] * parts_of[i]
+        item_part += list(range(parts_of[i]))
+    return item_token, item_part, parts_of, first_item
+
+
+@dataclass
+class DecodeItems:
+    """The work list of :func:`plan_decode_items` on the device (int32), padded to ``num_items`` items with -1."""
+
+    item_token: torch.Tensor
+    item_part: torch.Tensor
+    parts_of: torch.Tensor
+    first_item: torch.Tensor
+    num_items: int
 
 
 def build_step_batch(slices: Sequence[RequestSlice], num_groups: int, device: torch.device | str,
@@ -196,9 +247,17 @@ class StaticBatch:
     slice assignments and one host-to-device copy.
     """
 
-    def __init__(self, tokens: int, seqs: int, table_widths: Sequence[int], device: torch.device | str) -> None:
+    def __init__(self, tokens: int, seqs: int, table_widths: Sequence[int], device: torch.device | str,
+                 item_windows: Sequence[int | None] = (), item_targets: Sequence[int] = ()) -> None:
+        """``item_windows`` / ``item_targets``: for each cache group whose decode attention takes a work
+        list, its window (``None``: every key) and the number of parts all requests together are cut into."""
         self.tokens, self.seqs, self.widths = int(tokens), int(seqs), [int(w) for w in table_widths]
+        self.item_windows = [int(w) if w else 0 for w in item_windows]
+        self.item_targets = [int(t) for t in item_targets]
         counts = [tokens, tokens, tokens, seqs + 1, seqs, seqs, seqs] + [seqs * w for w in self.widths]
+        self._first_item_range = len(counts)
+        for target in self.item_targets:  # item_token, item_part, parts_of, first_item
+            counts += [seqs + target, seqs + target, seqs, seqs]
         total = sum(counts)
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()
@@ -207,12 +266,19 @@ class StaticBatch:
         for c in counts:
             offsets.append(offsets[-1] + c)
         self._ranges = list(zip(offsets[:-1], offsets[1:]))
-        for a, b in self._ranges[7:]:
+        for a, b in self._ranges[7:self._first_item_range]:
             self.host_np[a:b] = -1
+        for k in range(len(self.item_targets)):
+            a, b = self._ranges[self._first_item_range + 4 * k]
+            self.host_np[a:b] = -1  # no item is in use
         self._known: list[list[tuple[object, int]]] = [[(None, 0)] * seqs for _ in self.widths]
         self._uploaded: torch.cuda.Event | None = None
         views = [self.dev[a:b] for a, b in self._ranges]
         tables = [v.view(seqs, w) for v, w in zip(views[7:], self.widths)]
+        self._items = {}
+        for k, (window, target) in enumerate(zip(self.item_windows, self.item_targets)):
+            r = self._first_item_range + 4 * k
+            self._items[window] = DecodeItems(views[r], views[r + 1], views[r + 2], views[r + 3], seqs + target)
         self.batch = StepBatch(
             num_tokens=tokens, num_seqs=seqs, token_ids=views[0], positions=views[1], seq_of_token=views[2],
             query_start_loc=views[3], context_lens=views[4], block_tables=tables, state_slots=views[5],
@@ -268,11 +334,27 @@ class StaticBatch:
                 if known[i][0] is not None:
                     table[i] = -1
                     known[i] = (None, 0)
+        uneven = skew_class([p + 1 for p in starts]) >= WORK_LIST_FROM
+        if uneven:
+            for k, (window, target) in enumerate(zip(self.item_windows, self.item_targets)):
+                visible = [min(p + 1, window) if window else p + 1 for p in starts]
+                item_token, item_part, parts_of, first_item = plan_decode_items(visible, target)
+                r = self._first_item_range + 4 * k
+                host = [self._host(r + j) for j in range(4)]
+                host[0][: len(item_token)] = item_token
+                host[0][len(item_token):] = -1
+                host[1][: len(item_part)] = item_part
+                host[1][len(item_part):] = 0
+                host[2][:n] = parts_of
+                host[2][n:] = 1
+                host[3][:n] = first_item
+                host[3][n:] = 0
         self.dev.copy_(self.host, non_blocking=True)
         if self._uploaded is None:
             self._uploaded = torch.cuda.Event()
         self._uploaded.record()
         batch = self.batch
+        batch.decode_items = self._items if uneven else {}
         batch.query_lens_host = [1] * n
         batch.context_lens_host = [p + 1 for p in starts]
         batch.state_slots_host = [piece.state_slot for piece in slices]

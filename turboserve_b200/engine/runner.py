@@ -200,9 +200,11 @@ class ModelRunner:
         The kernels' grids depend on the batch size and the class alone, so the capture may run on
         a batch of padding tokens (which touch no page) as well as on the step that first needs it.
         """
-        static = StaticBatch(bucket, bucket, self._graph_widths, self.device)
+        static = StaticBatch(bucket, bucket, self._graph_widths, self.device, *self._decode_item_plan())
         static.load_decode(slices)
         static.batch.decode_skew = skew
+        if skew >= 4 and not static.batch.decode_items:
+            static.batch.decode_items = static._items  # a capture on padding tokens: the kernels still walk the (empty) lists
         if device_tokens is not None:
             static.batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
         stream = torch.cuda.Stream(device=self.device)
@@ -225,6 +227,18 @@ class ModelRunner:
         # the cache holds these tokens; replaying once more writes the same values again
         return entry
 
+    def _decode_item_plan(self) -> tuple[list[int | None], list[int]]:
+        """Per cache group: its window, and into how many parts the requests of a lopsided decode
+        step are cut together there (by the fewest kv heads of the group's layers)."""
+        from ..ops.attention_bf16 import decode_item_target
+        from ..ops.skinny import num_sms
+
+        targets = []
+        for g in range(len(self.plan.windows)):
+            heads = [run.need.num_kv_heads for run in self.plan.runs if run.kind == "paged" and run.group == g]
+            targets.append(decode_item_target(min(heads, default=1), num_sms(self.device)))
+        return list(self.plan.windows), targets
+
     def capture_decode_graphs(self, skew_classes: Sequence[int] = (1,)) -> int:
         """Capture the decode graphs of every batch-size bucket for the given classes now, so that
         no request meets a capture (a warm-up step, a synchronisation and the capture itself) in
@@ -241,9 +255,11 @@ class ModelRunner:
     @torch.inference_mode()
     def _replay_decode(self, slices: Sequence[RequestSlice], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         bucket = next(b for b in self._graph_buckets if b >= len(slices))
-        # the kernels' grids are part of a graph, and decode attention sizes its grid by how lopsided
-        # the batch is: one graph per (batch size, class), captured at start-up or when first needed
-        key = (bucket, skew_class([piece.start_position + 1 for piece in slices]))
+        # the kernels' grids are part of a graph, and decode attention has other grids for a lopsided
+        # batch: one graph per (batch size, class 1, 2 or "4 and up"), captured at start-up or when first needed
+        # classes 1 and 2 differ in the number of parts every request is cut into; from 4 on attention
+        # walks a work list made from the lengths: one graph serves them all
+        key = (bucket, min(4, skew_class([piece.start_position + 1 for piece in slices])))
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(bucket, key[1], slices, device_tokens)

@@ -127,6 +127,45 @@ def flash_decode_tma(q, out, k_pages, v_pages, block_table, seq_of_token, positi
            launches=2 if num_splits > CLUSTER_MAX_SPLITS else 1)
 
 
+WORK_LIST = os.environ.get("TURBOSERVE_B200_DECODE_WORK_LIST", "1") != "0"
+"""A very lopsided decode step (``StepBatch.decode_skew`` >= WORK_LIST_FROM) cuts every request into parts by its
+own length (a work list the TMA-fed kernel walks) instead of all requests into the same, larger, number of parts."""
+WORK_LIST_FROM = 4
+"""Measured at the 7B sizes: 64 requests, one at 32,768 tokens and 63 at 512 (class 16): 4.73 ms a step with
+the list, 5.0 ms with 16 times the parts for everyone; 16 requests, one at 8,192 and 15 at 1,024 (class 2):
+3.96 ms with the list, 3.80 ms with twice the parts, which still meet inside a cluster."""
+
+
+def decode_item_target(num_kv_heads: int, sms: int) -> int:
+    """Into how many parts the requests of a lopsided decode step are cut together: two rounds of
+    two blocks a multiprocessor, a block being (part, kv head)."""
+    return max(32, 2 * ((2 * sms) // max(1, num_kv_heads)))
+
+
+def flash_decode_tma_items(q, out, k_pages, v_pages, block_table, seq_of_token, positions, num_tokens, num_heads,
+                           num_kv_heads, head_dim, window, scale, items, scratch, status=None) -> None:
+    """Decode attention over a work list (``engine.batch.DecodeItems``): every request cut by its own length."""
+    _common(q, out, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim)
+    _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
+    for name in ("item_token", "item_part", "parts_of", "first_item"):
+        _need(getattr(items, name), torch.int32, name)
+    if items.item_token.numel() < items.num_items or items.item_part.numel() < items.num_items \
+            or items.parts_of.numel() < num_tokens or items.first_item.numel() < num_tokens:
+        raise KernelError("flash_decode_tma_items: the work list is shorter than it says")
+    _need(scratch, torch.float32, "scratch")
+    if scratch.numel() < items.num_items * num_heads * (head_dim + 2):
+        raise KernelError("flash_decode_tma_items: scratch is too small")
+    fn = _fn("attention_bf16", "ts_flash_decode_tma_items",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+              c_void_p, c_void_p])
+    _check(fn(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
+              _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens, k_pages.shape[1],
+              num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), _ptr(items.item_token), _ptr(items.item_part),
+              _ptr(items.parts_of), _ptr(items.first_item), int(items.num_items), _ptr(scratch), _ptr(status), _stream()),
+           "flash_decode_tma_items", launches=2)
+
+
 FUSED_CLUSTER = os.environ.get("TURBOSERVE_B200_FUSED_CLUSTER", "1") != "0"
 FUSED_DECODE = os.environ.get("TURBOSERVE_B200_FUSED_DECODE", "0") != "0"
 """With 1, decode steps let the TMA-fed attention kernel add the bias, rotate queries and keys and
@@ -259,9 +298,27 @@ def _decode_tokens(q, out, k_pages, v_pages, block_table, batch, first, n, num_h
     # (buffers may not grow once decode graphs have been captured)
     bound = num_heads * (head_dim + 2) * (n + SKEW_SPLIT_ROOM * ((2 * sms) // num_kv_heads) + 1)
     scratch = ctx.buffer("attn.decode_scratch", (bound,), torch.float32)
+    uneven = getattr(batch, "decode_skew", 1) >= WORK_LIST_FROM and first == 0 and n == batch.num_tokens
     if fusion is not None:
         flash_decode_tma_fused(q, fusion, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads,
                                num_kv_heads, head_dim, window, scale, splits, scratch, ctx.status)
+    elif WORK_LIST and uneven and TMA_DECODE and tma_decode_supports(head_dim, k_pages.shape[1], group):
+        items = getattr(batch, "decode_items", {}).get(int(window or 0))
+        if items is None:
+            # a batch that brought no list of its own (not one of fixed shape): make one from its lengths
+            from ..engine.batch import DecodeItems, plan_decode_items
+
+            visible = [min(c, window) if window else c for c in batch.context_lens_host]
+            target = decode_item_target(num_kv_heads, sms)
+            lists = plan_decode_items(visible, target)
+            count = len(lists[0])
+            flat = torch.tensor(lists[0] + lists[1] + lists[2] + [1] * (n - len(visible)) + lists[3] + [0] * (n - len(visible)),
+                                dtype=torch.int32).to(q.device, non_blocking=True)
+            items = DecodeItems(flat[:count], flat[count:2 * count], flat[2 * count:2 * count + n], flat[2 * count + n:], count)
+            if isinstance(getattr(batch, "decode_items", None), dict):
+                batch.decode_items[int(window or 0)] = items  # the other layers of the step use it too
+        flash_decode_tma_items(q, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads, num_kv_heads,
+                               head_dim, window, scale, items, scratch, ctx.status)
     elif TMA_DECODE and tma_decode_supports(head_dim, k_pages.shape[1], group):
         flash_decode_tma(q, out, k_pages, v_pages, block_table, seq_of_token, positions, n, num_heads,
                          num_kv_heads, head_dim, window, scale, splits, scratch, ctx.status)
