@@ -146,7 +146,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
               const int* __restrict__ history, const int* __restrict__ history_start,
               int* __restrict__ tokens, float* __restrict__ logprobs, const int* __restrict__ row_slot,
               const int* __restrict__ row_seq, const int* __restrict__ row_context,
-              const int* __restrict__ prompt_len, int* __restrict__ partial) {
+              const int* __restrict__ prompt_len, int* __restrict__ partial, int skip_filtered) {
   pdl_wait();
   pdl_trigger();
   __shared__ ArgMax arg_scratch[33];
@@ -218,6 +218,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
     return;
   }
   if (blockIdx.y != 0) return;  // a row that needs more than one pass is its first block's alone
+  if (skip_filtered && row_slot && pen == 1.0f && !need_lse && temp > 0.0f) return;  // the cluster kernel that follows draws it
 
   // -- repetition penalty ---------------------------------------------------------------
   for (int i = tid; i < vocab; i += blockDim.x) w[i] = x[i];
@@ -430,6 +431,203 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Rows that need the filters (top-k, top-p), worked by a cluster of blocks instead of one block:
+// block r of a row's cluster keeps part r of the row, divided by the temperature, in its shared
+// memory; every radix pass builds a histogram per block, the blocks read one another's over
+// distributed shared memory after a cluster barrier and each walks the sum (the same integers
+// in every block, so they all choose the same bin).  The counts and the fixed-point masses are
+// exact integers, so the ids are those of the one-block path above, which scans the row in
+// global memory eleven times.  Options by state slot, as ts_sample_slots gives them; rows that
+// need no filter (or are padding, or marked to be left alone) are not touched: the whole cluster
+// leaves at once.
+// ---------------------------------------------------------------------------------------------
+#define SAMPLE_CLUSTER 8
+__device__ __forceinline__ void sample_cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned int sample_remote(const void* local, int rank) {
+  unsigned int remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"((unsigned int)__cvta_generic_to_shared(local)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ unsigned int sample_remote_u32(const void* local, int rank) {
+  unsigned int v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(sample_remote(local, rank)));
+  return v;
+}
+__device__ __forceinline__ unsigned long long sample_remote_u64(const void* local, int rank) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(sample_remote(local, rank)));
+  return v;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride, int vocab, int per,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
+                      const int* __restrict__ prompt_len, const int* __restrict__ row_slot,
+                      const int* __restrict__ row_seq, const int* __restrict__ row_context,
+                      int* __restrict__ tokens) {
+  pdl_wait();
+  extern __shared__ float w[];  // this block's part of the row: `per` values
+  __shared__ ArgMax arg_scratch[33];
+  __shared__ float f_scratch[33];
+  __shared__ unsigned int hist32[256];        // what the others read: this block's counts per bin
+  __shared__ unsigned long long hist64[256];  // and its masses per bin
+  __shared__ unsigned long long total64[256];
+  __shared__ unsigned int total32[256];
+  __shared__ unsigned long long hist_copies[HIST_COPIES * 256];
+  unsigned int* const hist_copies32 = reinterpret_cast<unsigned int*>(hist_copies);
+  __shared__ float local_max;
+  __shared__ ArgMax local_best;
+  __shared__ unsigned int sel_prefix, sel_remaining;
+  __shared__ unsigned long long sel_above;
+
+  const int row = blockIdx.y, rank = blockIdx.x, tid = threadIdx.x;  // the cluster lies along x
+  const int copy = tid & (HIST_COPIES - 1);
+  if (row_seq && row_seq[row] < 0) return;
+  const int opt = row_slot[row];
+  const float temp = temperature[opt];
+  const int k = top_k ? top_k[opt] : 0;
+  const float p_keep = top_p ? top_p[opt] : 1.0f;
+  const bool use_k = k > 0 && k < vocab, use_p = p_keep < 1.0f;
+  if (!(temp > 0.0f) || (!use_k && !use_p)) return;  // not a row for this kernel (the same in every block of the cluster)
+  const unsigned long long sd = seed ? seed[opt] : 0ull;
+  const unsigned int ctr = (unsigned int)(row_context[row] - prompt_len[opt]);
+
+  const int lo = min(vocab, rank * per), count = min(vocab, lo + per) - lo;
+  const float* x = logits + (size_t)row * logits_stride + lo;
+  for (int i = tid; i < count; i += blockDim.x) w[i] = x[i] / temp;
+  __syncthreads();
+
+  if (use_k) {
+    if (tid == 0) { sel_prefix = 0; sel_remaining = (unsigned int)k; }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = tid; b < HIST_COPIES * 256; b += blockDim.x) hist_copies32[b] = 0;
+      __syncthreads();
+      const unsigned int prefix = sel_prefix;
+      const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < count; i += blockDim.x) {
+        const unsigned int key = ordered_key(w[i]);
+        if ((key & mask) != prefix) continue;
+        atomicAdd(&hist_copies32[copy * 256 + ((key >> shift) & 255u)], 1u);
+      }
+      __syncthreads();
+      for (int b = tid; b < 256; b += blockDim.x) {
+        unsigned int sum = 0u;
+#pragma unroll
+        for (int c = 0; c < HIST_COPIES; ++c) sum += hist_copies32[c * 256 + b];
+        hist32[b] = sum;
+      }
+      sample_cluster_barrier();  // every block's counts are in place
+      for (int b = tid; b < 256; b += blockDim.x) {
+        unsigned int sum = 0u;
+#pragma unroll
+        for (int r = 0; r < SAMPLE_CLUSTER; ++r) sum += sample_remote_u32(&hist32[b], r);
+        total32[b] = sum;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned int remaining = sel_remaining;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (total32[b] >= remaining) break;
+          remaining -= total32[b];
+        }
+        sel_prefix = prefix | ((unsigned int)b << shift);
+        sel_remaining = remaining;
+      }
+      sample_cluster_barrier();  // all have read the counts before the next pass overwrites them
+    }
+    const float threshold = key_to_float(sel_prefix);
+    for (int i = tid; i < count; i += blockDim.x)
+      if (w[i] < threshold) w[i] = -INFINITY;
+    __syncthreads();
+  }
+
+  if (use_p) {
+    float mx = -INFINITY;
+    for (int i = tid; i < count; i += blockDim.x) mx = fmaxf(mx, w[i]);
+    mx = block_max(mx, f_scratch);
+    if (tid == 0) local_max = mx;
+    sample_cluster_barrier();
+    for (int r = 0; r < SAMPLE_CLUSTER; ++r) mx = fmaxf(mx, __uint_as_float(sample_remote_u32(&local_max, r)));
+    const float fixed_one = 1099511627776.0f;  // 2^40
+    if (tid == 0) { sel_prefix = 0; sel_above = 0ull; }
+    unsigned long long limit = 0ull;
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = tid; b < HIST_COPIES * 256; b += blockDim.x) hist_copies[b] = 0ull;
+      __syncthreads();
+      const unsigned int prefix = sel_prefix;
+      const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < count; i += blockDim.x) {
+        const float v = w[i];
+        if (v == -INFINITY) continue;
+        const unsigned int key = ordered_key(v);
+        if ((key & mask) != prefix) continue;
+        atomicAdd(&hist_copies[copy * 256 + ((key >> shift) & 255u)], (unsigned long long)(expf(v - mx) * fixed_one));
+      }
+      __syncthreads();
+      for (int b = tid; b < 256; b += blockDim.x) {
+        unsigned long long sum = 0ull;
+#pragma unroll
+        for (int c = 0; c < HIST_COPIES; ++c) sum += hist_copies[c * 256 + b];
+        hist64[b] = sum;
+      }
+      sample_cluster_barrier();
+      for (int b = tid; b < 256; b += blockDim.x) {
+        unsigned long long sum = 0ull;
+#pragma unroll
+        for (int r = 0; r < SAMPLE_CLUSTER; ++r) sum += sample_remote_u64(&hist64[b], r);
+        total64[b] = sum;
+      }
+      __syncthreads();
+      if (tid == 0) {  // `limit` lives in thread 0 alone: only it walks the histogram
+        if (shift == 24) {
+          unsigned long long total = 0ull;
+          for (int b = 0; b < 256; ++b) total += total64[b];
+          limit = (unsigned long long)((double)p_keep * (double)total);
+        }
+        unsigned long long above = sel_above;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (above + total64[b] > limit) break;
+          above += total64[b];
+        }
+        sel_prefix = prefix | ((unsigned int)b << shift);
+        sel_above = above;
+      }
+      sample_cluster_barrier();
+    }
+    const float threshold = key_to_float(sel_prefix);
+    for (int i = tid; i < count; i += blockDim.x)
+      if (w[i] < threshold) w[i] = -INFINITY;
+    __syncthreads();
+  }
+
+  ArgMax pick{-INFINITY, 0x7fffffff};
+  for (int i = tid; i < count; i += blockDim.x) {
+    const float v = w[i];
+    if (v == -INFINITY) continue;
+    const float u = sample_uniform(sd, ctr, (unsigned int)(lo + i));
+    pick = better(pick, ArgMax{v - logf(-logf(u)), lo + i});
+  }
+  pick = block_argmax(pick, arg_scratch);
+  if (tid == 0) local_best = pick;
+  sample_cluster_barrier();
+  if (rank == 0 && tid == 0) {
+    ArgMax all{-INFINITY, 0x7fffffff};
+    for (int r = 0; r < SAMPLE_CLUSTER; ++r)
+      all = better(all, ArgMax{__uint_as_float(sample_remote_u32(&local_best.value, r)), (int)sample_remote_u32(&local_best.index, r)});
+    tokens[row] = all.index;
+  }
+  sample_cluster_barrier();  // nobody leaves while its shared memory may still be read
+}
+
 // All per-row arrays may be null, which means: greedy, no filter, no penalty, seed 0.
 TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* work, int num_rows,
                         int vocab, const float* temperature, const int* top_k, const float* top_p,
@@ -441,7 +639,7 @@ TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* wor
   if (work == nullptr || tokens == nullptr) return TS_ERR_ARGUMENT;
   ts_launch(sample_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
             temperature, top_k, top_p, penalty, seed, counter, history, history_start, tokens, logprobs,
-            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr);
+            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr, 0);
   return ts_launch_status();
 }
 
@@ -464,9 +662,20 @@ TS_EXPORT int ts_sample_slots(const float* logits, long long logits_stride, floa
   if (work == nullptr || tokens == nullptr || row_slot == nullptr || row_context == nullptr || prompt_len == nullptr ||
       temperature == nullptr || partial == nullptr)
     return TS_ERR_ARGUMENT;
+  // rows with top-k or top-p go to a cluster of blocks that holds the row in shared memory, when it fits there
+  const int per = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + 3) / 4 * 4;
+  const size_t cluster_smem = (size_t)per * sizeof(float);
+  const bool clustered = (top_k != nullptr || top_p != nullptr) && cluster_smem <= 180 * 1024 && num_rows <= 65535;
   ts_launch(sample_kernel, dim3(num_rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
             temperature, top_k, top_p, (const float*)nullptr, seed, (const unsigned int*)nullptr, (const int*)nullptr,
-            (const int*)nullptr, tokens, (float*)nullptr, row_slot, row_seq, row_context, prompt_len, partial);
+            (const int*)nullptr, tokens, (float*)nullptr, row_slot, row_seq, row_context, prompt_len, partial,
+            clustered ? 1 : 0);
+  int code = ts_launch_status();
+  if (code || !clustered) return code;
+  cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cluster_smem);
+  ts_launch_cluster(sample_cluster_kernel, dim3(SAMPLE_CLUSTER, num_rows), dim3(SAMPLE_THREADS), cluster_smem, stream,
+                    SAMPLE_CLUSTER, logits, logits_stride, vocab, per, temperature, top_k, top_p, seed, prompt_len, row_slot,
+                    row_seq, row_context, tokens);
   return ts_launch_status();
 }
 

@@ -295,7 +295,7 @@ def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
     fn = _fn("sampling", "ts_sample_slots", [c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 10 + [c_int, c_void_p])
     _check(fn(_ptr(logits), logits.stride(0), _ptr(work), num_rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
               _ptr(seed), _ptr(prompt_len), _ptr(row_slot), _ptr(row_seq), _ptr(row_context), _ptr(tokens), _ptr(partial),
-              int(chunks), _stream()), "sample_slots")
+              int(chunks), _stream()), "sample_slots", launches=2)  # the one-pass kernel, then the cluster kernel for rows with filters
 
 
 def sample_uniform_host(seed: int, counter: int, index: int) -> float:
