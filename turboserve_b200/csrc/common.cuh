@@ -95,7 +95,8 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 //   add + norm (dependents: the qkv and gate/up products, which fetch weights first)   3.33 ms
 //   register-streaming products (dependents: element-wise kernels)                      3.37 ms
 //   decode attention, register-fed kernel (dependent: the output projection)            3.39 ms
-//     (the TMA-fed decode kernel does not trigger: 3.42 ms with, 3.21 ms without)
+//     (the TMA-fed decode kernel does not trigger: 3.42 ms with, 3.21 ms without; triggering after
+//     its last key tile, before the join of its parts, costs as much: 3.49 against 3.28 ms)
 //   rotation + cache append (dependent: decode attention, launched as clusters)         3.76 ms
 //     (with attention launched without clusters the same trigger costs 0.02 ms: it is the
 //     early launch of a cluster kernel that is slow)
