@@ -448,6 +448,101 @@ def fp32_products() -> int:
     return 0
 
 
+def decode_attention_sweep() -> int:
+    """The TMA-fed decode attention kernel alone at a few (requests, keys, parts): µs and TB/s of keys and
+    values, CUDA events around a graph of "write 256 MB, run the kernel" with the write alone subtracted."""
+    import torch
+
+    from turboserve_b200.ops import attention_bf16 as fa
+
+    nh, nkv, d, page = 28, 4, 128, PAGE
+    flush = torch.empty(256 * 1024 * 1024 // 4, device="cuda")
+    rows = []
+
+    def timed(graph) -> float:
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(20):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / 20 * 1e3
+
+    empty = torch.cuda.CUDAGraph()
+    flush.zero_()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(empty):
+        flush.zero_()
+    base = timed(empty)
+    for batch, ctx, parts in [(8, 4096, 8), (8, 4096, 9), (64, 512, 1), (32, 1024, 1), (32, 1024, 2), (8, 16384, 8),
+                              (64, 4096, 1), (1, 4096, 8), (1, 4096, 32)]:
+        width = ctx // page + 1
+        k_pages = torch.randn(batch * width, page, nkv, d, device="cuda").to(torch.bfloat16)
+        v_pages = torch.randn(batch * width, page, nkv, d, device="cuda").to(torch.bfloat16)
+        table = torch.arange(batch * width, dtype=torch.int32, device="cuda").view(batch, width)
+        q = torch.randn(batch, nh * d, device="cuda").to(torch.bfloat16)
+        out = torch.empty_like(q)
+        seq = torch.arange(batch, dtype=torch.int32, device="cuda")
+        pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device="cuda")
+        scratch = torch.empty(max(4, fa.decode_scratch_floats(batch, nh, parts, d)), device="cuda")
+
+        def run():
+            fa.flash_decode_tma(q, out, k_pages, v_pages, table, seq, pos, batch, nh, nkv, d, None, d ** -0.5, parts, scratch)
+
+        run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            flush.zero_()
+            run()
+        us = timed(graph) - base
+        rows.append({"requests": batch, "keys": ctx, "parts": parts, "us": round(us, 1),
+                     "tb_per_s": round(batch * ctx * nkv * d * 4 / us / 1e6, 2)})
+        del k_pages, v_pages
+    print(json.dumps({"what": "flash_decode_tma alone, 28 heads on 4 kv heads of 128, pages of 16", "rows": rows}))
+    return 0
+
+
+def sampling_sweep(context: int = 4096, steps: int = 40) -> int:
+    """Decode steps of 8 requests through LLMEngine.step() under a few sets of sampling options: ms a step each."""
+    import torch
+
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    config, model, runner = build_runner(SHAPES["7b"][1]["num_hidden_layers"], 8, context)
+    runner.enable_graphs(8, context, 2048)
+    line = {"what": "ms a decode step through LLMEngine.step(), 7B sizes, batch 8", "context": context, "steps": steps}
+    for name, options in [("greedy", dict(temperature=0.0)), ("temperature", dict(temperature=0.8, seed=1)),
+                          ("top_p", dict(temperature=0.8, top_p=0.9, seed=1)),
+                          ("top_k_top_p", dict(temperature=0.8, top_p=0.9, top_k=50, seed=1)),
+                          ("penalty", dict(temperature=0.8, top_p=0.9, top_k=50, seed=1, repetition_penalty=1.2)),
+                          ("greedy_again", dict(temperature=0.0))]:
+        engine = LLMEngine(EngineConfig(model="(injected)", dtype="bfloat16", max_model_len=context, scheduler=SchedulerConfig(
+            max_num_seqs=8, max_num_batched_tokens=2048, block_size=PAGE, num_blocks=runner.groups[0].num_pages)), runner=runner)
+        generator = torch.Generator().manual_seed(2)
+        sampling = SamplingParams(max_tokens=steps + 40, ignore_eos=True, **options)
+        for i in range(8):
+            engine.add_request(f"r{i}", torch.randint(0, config.vocab_size, (context - steps - 100,), generator=generator).tolist(), sampling)
+        while any(seq.num_output_tokens == 0 for seq in engine.scheduler._running) or engine.scheduler.num_waiting:
+            engine.step()
+        for _ in range(5):
+            engine.step()
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += sum(len(o.new_token_ids) for o in engine.step())
+        torch.cuda.synchronize()
+        line[name] = round((time.perf_counter() - started) / steps * 1e3, 3)
+        if produced != 8 * steps:
+            raise RuntimeError(f"{name}: {produced} tokens in {steps} steps")
+        engine.close()
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -465,6 +560,8 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT,
                         help="context length of the decode runs (the headline is 4096; others are for sweeps)")
     parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
+    parser.add_argument("--decode-attention-sweep", action="store_true", help="time the decode attention kernel alone at a few sizes and exit")
+    parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                         help="run three eager steps of that kind and exit (a small case for a profiler)")
@@ -487,6 +584,10 @@ def main() -> int:
 
     if args.fp32_products:
         return fp32_products()
+    if args.decode_attention_sweep:
+        return decode_attention_sweep()
+    if args.sampling_sweep:
+        return sampling_sweep()
     if args.one_step:
         return one_step(args.one_step, args.layers, args.batch, args.shape)
     if args.scenario:
