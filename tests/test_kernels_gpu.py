@@ -935,3 +935,22 @@ def test_decode_attention_over_a_work_list(nh, nkv, page, window):
     got = out[:live].view(live, nh, d).double().cpu()
     assert torch.isfinite(got).all() and torch.isnan(out[live:].float()).all()
     assert (got - ref).abs().max().item() < 2e-2, (got - ref).abs().max().item()
+
+
+def test_the_two_tilings_of_the_float32_product_give_the_same_bits():
+    """Rows 0..63 of a product of 200 rows (the 128x128 tiling) equal the product of those 64 rows alone
+    (the 64x64 tiling) bit for bit, at sizes that are no multiple of any tile and with unaligned rows."""
+    from turboserve_b200.ops import kernels
+
+    torch.manual_seed(9)
+    for k, n, pad in [(200, 150, 0), (1030, 257, 0), (77, 130, 3), (3584, 520, 0)]:
+        a = torch.randn(200, k + pad, device=DEV)[:, :k]   # pad: a row stride that is no multiple of four
+        w = torch.randn(n, k + pad, device=DEV)[:, :k] / math.sqrt(k)
+        bias = torch.randn(n, device=DEV)
+        big = torch.empty(200, n, device=DEV)
+        small = torch.empty(64, n, device=DEV)
+        kernels.gemm_simt(a, w, big, bias)
+        kernels.gemm_simt(a[:64], w, small, bias, 64)
+        assert torch.equal(big[:64], small), (k, n, pad)
+        ref = a.double() @ w.double().T + bias.double()
+        assert (big.double() - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())

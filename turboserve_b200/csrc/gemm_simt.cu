@@ -2,9 +2,13 @@
 // product of the true 32-bit path (no TF32, no tensor cores), also taken by bf16 shapes
 // that the tensor-core kernels refuse.  Any M, N, K.
 //
-// 64x64 output tile per block, 16-wide K steps staged in shared memory, a 4x4 micro-tile per
-// thread.  Every output element accumulates its K products in increasing k, one FFMA each,
-// so a row's result does not depend on M or on which tile the row falls into.
+// Two tilings of one kernel.  Up to 64 rows: a 64x64 output tile per block, 16-wide K steps
+// staged in shared memory, a 4x4 micro-tile per thread.  More rows (prompts on the float32
+// path): a 128x128 tile, an 8x8 micro-tile per thread, the next K step fetched into registers
+// (16 bytes at a time where rows are aligned) while the current one is multiplied, two buffers
+// of shared memory.  In both every output element accumulates its K products in increasing k,
+// one FFMA each, so a row's result does not depend on M, on the tiling or on which tile the row
+// falls into: the two give the same bits.
 // It stands where the reference calls F.linear (src/turboserve/engine/model/layers.py:142).
 #include "common.cuh"
 
@@ -70,24 +74,132 @@ gemm_simt_kernel(const TIn* __restrict__ a, long long lda, const TIn* __restrict
   }
 }
 
+// The 128x128 tiling (see the head of the file).  256 threads: thread (ty, tx) owns rows
+// ty * 8 .. + 7 and columns tx * 4 .. + 3 and 64 + tx * 4 .. + 3 of the tile (two runs of four, so
+// that a warp's reads of the weights' tile fall into different banks).
+#define LM 128
+#define LN 128
+#define LK 16
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+gemm_simt_large_kernel(const TIn* __restrict__ a, long long lda, const TIn* __restrict__ w,
+                       long long ldw, const float* __restrict__ bias, TOut* __restrict__ c,
+                       long long ldc, int m, int n, int k, int vector_ok) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ __align__(16) float a_s[2][LK][LM + 4];
+  __shared__ __align__(16) float w_s[2][LK][LN + 4];
+  const int tid = threadIdx.x;
+  const int tile_m = blockIdx.y * LM, tile_n = blockIdx.x * LN;
+  const int tx = tid % 16, ty = tid / 16;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+  // a tile is 128 rows x 16 k: thread t fetches k 4 * (t % 4) .. + 3 of rows t / 4 and 64 + t / 4
+  const int load_row = tid / 4, load_k = (tid % 4) * 4;
+  float ra[2][4], rw[2][4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int am = tile_m + load_row + 64 * h, wn = tile_n + load_row + 64 * h;
+      const int kk = k0 + load_k;
+      if (vector_ok && kk + 3 < k) {
+        float4 va = make_float4(0.0f, 0.0f, 0.0f, 0.0f), vw = va;
+        if (am < m) va = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a) + (size_t)am * lda + kk);
+        if (wn < n) vw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + (size_t)wn * ldw + kk);
+        ra[h][0] = va.x; ra[h][1] = va.y; ra[h][2] = va.z; ra[h][3] = va.w;
+        rw[h][0] = vw.x; rw[h][1] = vw.y; rw[h][2] = vw.z; rw[h][3] = vw.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          ra[h][e] = (am < m && kk + e < k) ? to_float(a[(size_t)am * lda + kk + e]) : 0.0f;
+          rw[h][e] = (wn < n && kk + e < k) ? to_float(w[(size_t)wn * ldw + kk + e]) : 0.0f;
+        }
+      }
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        a_s[buf][load_k + e][load_row + 64 * h] = ra[h][e];
+        w_s[buf][load_k + e][load_row + 64 * h] = rw[h][e];
+      }
+  };
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < k; k0 += LK) {
+    const bool more = k0 + LK < k;
+    if (more) fetch(k0 + LK);  // in flight while this step is multiplied
+#pragma unroll
+    for (int kk = 0; kk < LK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&a_s[buf][kk][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&a_s[buf][kk][ty * 8 + 4]);
+      const float4 w0 = *reinterpret_cast<const float4*>(&w_s[buf][kk][tx * 4]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&w_s[buf][kk][64 + tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    if (more) {
+      stage(buf ^ 1);  // the other buffer: nobody reads it during this step
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = tile_m + ty * 8 + i;
+    if (row >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int col = tile_n + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (col >= n) continue;
+      float v = acc[i][j];
+      if (bias) v += bias[col];
+      c[(size_t)row * ldc + col] = from_float<TOut>(v);
+    }
+  }
+}
+
+template <typename TIn, typename TOut>
+static void launch_simt(const void* a, long long lda, const void* w, long long ldw, const float* bias, void* c,
+                        long long ldc, int m, int n, int k, cudaStream_t stream) {
+  if (m > BM) {
+    const bool fp32 = sizeof(TIn) == 4;
+    const int vector_ok = fp32 && lda % 4 == 0 && ldw % 4 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15);
+    dim3 grid((n + LN - 1) / LN, (m + LM - 1) / LM);
+    ts_launch(gemm_simt_large_kernel<TIn, TOut>, grid, dim3(256), 0, stream, (const TIn*)a, lda, (const TIn*)w, ldw,
+              bias, (TOut*)c, ldc, m, n, k, vector_ok);
+    return;
+  }
+  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+  ts_launch(gemm_simt_kernel<TIn, TOut>, grid, dim3(256), 0, stream, (const TIn*)a, lda, (const TIn*)w, ldw, bias,
+            (TOut*)c, ldc, m, n, k);
+}
+
 // out_dtype: dtype code of C (TS_F32 is allowed with bf16 inputs: logits).
 TS_EXPORT int ts_gemm_simt(int dtype, int out_dtype, const void* a, long long lda, const void* w,
                            long long ldw, const float* bias, void* c, long long ldc, int m, int n,
                            int k, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k < 0) return TS_ERR_SIZE;
-  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
-  if (grid.y > 65535) return TS_ERR_SIZE;
+  if ((m + BM - 1) / BM > 65535) return TS_ERR_SIZE;
   if (dtype == TS_F32 && out_dtype == TS_F32)
-    ts_launch(gemm_simt_kernel<float, float>, dim3(grid), dim3(256), 0, stream, 
-        (const float*)a, lda, (const float*)w, ldw, bias, (float*)c, ldc, m, n, k);
+    launch_simt<float, float>(a, lda, w, ldw, bias, c, ldc, m, n, k, stream);
   else if (dtype == TS_BF16 && out_dtype == TS_BF16)
-    ts_launch(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 
-        (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias, (__nv_bfloat16*)c, ldc,
-        m, n, k);
+    launch_simt<__nv_bfloat16, __nv_bfloat16>(a, lda, w, ldw, bias, c, ldc, m, n, k, stream);
   else if (dtype == TS_BF16 && out_dtype == TS_F32)
-    ts_launch(gemm_simt_kernel<__nv_bfloat16, float>, dim3(grid), dim3(256), 0, stream, 
-        (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias, (float*)c, ldc, m, n, k);
+    launch_simt<__nv_bfloat16, float>(a, lda, w, ldw, bias, c, ldc, m, n, k, stream);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();
