@@ -46,6 +46,11 @@
 // overall (2,048 tokens: 114 to 124 us against 85 us; with try_wait, with a test_wait spin, with
 // a short suspend hint): the waits of the other kind grew by more than these shrank.
 //
+// Tried and dropped too: the two warps of a row pair meeting at a named hardware barrier of their own
+// (bar.red.and over 64 threads, which also carries "nobody has given up", one meeting a tile with
+// the exchanged numbers in two buffers) instead of the two mbarriers: correct, and slower
+// (2,048 tokens: 83.5 us against 74; 8,192: 813 against 688).
+//
 // Every mbarrier wait is bounded; a wait that runs out raises bit 32 of *status, the block stops,
 // frees its tensor memory and returns.  No cluster, no multicast.
 // Replaces the reference's per-sequence gather + SDPA (src/turboserve/engine/model/
