@@ -51,6 +51,23 @@
 // the exchanged numbers in two buffers) instead of the two mbarriers: correct, and slower
 // (2,048 tokens: 83.5 us against 74; 8,192: 813 against 688).
 //
+// Tried and dropped: a second form of the kernel after the published Blackwell attention designs: a
+// block alone on its multiprocessor with TWO row tiles that take turns on the tensor cores, key
+// tiles of 128, one softmax thread per row with all 128 scores in registers (no exchange between
+// threads), and P written back into tensor memory over the scores (tcgen05.st of packed bfloat16
+// pairs, column c = keys 2c and 2c + 1) and read from there as the A operand of the O product
+// (tcgen05.mma with [a_taddr]: exact in a one-block probe and in the kernel's tests).  Correct on
+// every shape of the tests, bit-stable, and slower: 2,048 tokens 92 us against 70, 8,192 944
+// against 648, 16,384 3,553 against 2,404 (542 against 800 TFLOP/s).  A trace of its softmax
+// threads: per 128-key step 2,400 to 3,100 cycles waiting for the scores, 700 to 900 for one round
+// of tcgen05.ld + wait, 5,200 to 5,900 for maximum, exponentials, packing and the store: eight
+// softmax warps a multiprocessor (two per scheduler) do not hide the latency of their own chains,
+// where the two blocks of the kernel above bring sixteen.  Reading the scores twice (the maximum
+// first, 32 at a time, to keep fewer registers) was worse still (344 TFLOP/s): every round of
+// tcgen05.ld + wait costs 700 to 1,200 cycles while the tensor cores run the other tile.  It
+// would take what the published designs add on top (exponentials partly as polynomials on the
+// FMA pipes, a correction warp group, more stages).
+//
 // Every mbarrier wait is bounded; a wait that runs out raises bit 32 of *status, the block stops,
 // frees its tensor memory and returns.  No cluster, no multicast.
 // Replaces the reference's per-sequence gather + SDPA (src/turboserve/engine/model/
