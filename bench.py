@@ -518,6 +518,9 @@ def sampling_sweep(context: int = 4096, steps: int = 40) -> int:
                           ("top_p", dict(temperature=0.8, top_p=0.9, seed=1)),
                           ("top_k_top_p", dict(temperature=0.8, top_p=0.9, top_k=50, seed=1)),
                           ("penalty", dict(temperature=0.8, top_p=0.9, top_k=50, seed=1, repetition_penalty=1.2)),
+                          ("greedy_penalty", dict(temperature=0.0, repetition_penalty=1.2)),
+                          ("greedy_logprobs", dict(temperature=0.0, logprobs=True)),
+                          ("top_p_penalty_logprobs", dict(temperature=0.8, top_p=0.9, seed=1, repetition_penalty=1.2, logprobs=True)),
                           ("greedy_again", dict(temperature=0.0))]:
         engine = LLMEngine(EngineConfig(model="(injected)", dtype="bfloat16", max_model_len=context, scheduler=SchedulerConfig(
             max_num_seqs=8, max_num_batched_tokens=2048, block_size=PAGE, num_blocks=runner.groups[0].num_pages)), runner=runner)

@@ -24,6 +24,7 @@ class HostRunner:
         self.model = self.Model()
         self.model.spec = self.Spec()
         self.token_buffer = torch.zeros(slots + 1, dtype=torch.int32)
+        self.token_out = self.token_buffer[:slots]
         self.fail_reads = 0
         self.steps = []
 

@@ -135,51 +135,87 @@ def test_temperature_sampling_matches_the_plain_sampler(model_folders, name):
             assert abs(out.logprobs[i] - logprob) < 1e-4
 
 
-def test_bfloat16_sampled_rows_match_the_plain_sampler_on_the_engines_own_logits(model_folders):
-    """Temperature, top-k, top-p and a penalty in bfloat16, with decode steps replayed from graphs that
-    end with the sampler (options by state slot) and launched ahead: every sampled id is what the
-    plain sampler draws from the very row of logits the step produced (exact ids), so a fault of
-    the sampler, of the slot arrays or of the token's index cannot hide behind bfloat16 rounding."""
-    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
-
-    config, _ = P.read_model_folder(model_folders["D"])
-    prompts = prompts_for(config, [9, 31, 60, 4], seed=12)
-    options = [dict(temperature=0.7, seed=11), dict(temperature=1.2, top_k=20, top_p=0.9, seed=5),
-               dict(temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3), dict(temperature=1.0, top_p=0.95)]
-    engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="bfloat16", seed=3, scheduler=SchedulerConfig(
-        max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)))
-    launched, checked, in_graph = [], [0], [0]
+def check_sampling_against_the_plain_sampler(engine):
+    """Hook an engine so that every sampled id (and log-probability) is compared with what the plain
+    sampler draws from the very row of logits the step produced. Returns the counters
+    ``{"checked", "in_graph", "logprobs"}``, which go up as the engine runs."""
+    launched, counts = [], {"checked": 0, "in_graph": 0, "logprobs": 0}
     run_step, process = engine.runner.step, engine._process
 
     def recording_step(slices, device_tokens=None):
         logits = run_step(slices, device_tokens)
         launched.append(None if logits is None else logits.clone())
-        in_graph[0] += int(engine.runner.sampled_in_graph)
+        counts["in_graph"] += int(engine.runner.sampled_in_graph)
         return logits
 
     def checking_process(plan, result):
         logits = launched.pop(0)  # steps are processed in the order they were launched
         if result is not None:
-            for row, seq, token in zip(logits.cpu(), plan.sampling_seqs(), result.token_ids):
+            for index, (row, seq, token) in enumerate(zip(logits.cpu(), plan.sampling_seqs(), result.token_ids)):
                 if seq.is_finished:
                     continue
                 params = seq.sampling
-                expect, _ = P.sample_token(row, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
-                                           repetition_penalty=params.repetition_penalty, history=seq.token_ids, seed=seq.seed,
-                                           counter=seq.num_output_tokens)
+                expect, logprob = P.sample_token(row, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
+                                                 repetition_penalty=params.repetition_penalty, history=seq.token_ids, seed=seq.seed,
+                                                 counter=seq.num_output_tokens)
                 assert token == expect, (seq.request_id, seq.num_output_tokens, token, expect)
-                checked[0] += 1
+                if params.logprobs:
+                    assert abs(result.logprobs[index] - logprob) < 1e-4, (seq.request_id, seq.num_output_tokens)
+                    counts["logprobs"] += 1
+                counts["checked"] += 1
         return process(plan, result)
 
     engine.runner.step, engine._process = recording_step, checking_process
+    return counts
+
+
+def test_bfloat16_sampled_rows_match_the_plain_sampler_on_the_engines_own_logits(model_folders):
+    """Temperature, top-k, top-p, penalties and log-probabilities in bfloat16, with decode steps replayed
+    from graphs that end with the sampler (options and histories by state slot) and launched ahead:
+    every sampled id is what the plain sampler draws from the very row of logits the step produced
+    (exact ids), so a fault of the sampler, of the slot arrays, of the history bitmap or of the
+    token's index cannot hide behind bfloat16 rounding."""
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    config, _ = P.read_model_folder(model_folders["D"])
+    prompts = prompts_for(config, [9, 31, 60, 4, 17], seed=12)
+    options = [dict(temperature=0.7, seed=11), dict(temperature=1.2, top_k=20, top_p=0.9, seed=5, logprobs=True),
+               dict(temperature=0.9, top_p=0.8, seed=7, repetition_penalty=1.3), dict(temperature=1.0, top_p=0.95),
+               dict(temperature=0.0, repetition_penalty=1.8, logprobs=True)]
+    engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="bfloat16", seed=3, scheduler=SchedulerConfig(
+        max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)))
+    counts = check_sampling_against_the_plain_sampler(engine)
     with engine:
         assert engine.runner.graph_sampler is engine.sampler and engine.sampler.slots is not None
-        # the request with a penalty (which no step can be launched ahead of) ends early; the others go on
-        lengths = [14, 14, 6, 14]
+        lengths = [14, 14, 14, 14, 14]
         outputs = engine.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True, **o) for n, o in zip(lengths, options)])
-        assert engine.stats()["num_overlapped_steps"] > 0 and engine.runner.num_graph_replays > 0 and in_graph[0] > 0
+        stats = engine.stats()
+        # every decode step sampled itself, and all but the first were launched ahead of the ids before them
+        assert counts["in_graph"] == 13 and stats["num_overlapped_steps"] >= 10 and engine.runner.num_graph_replays == 13
     assert [o.output_tokens for o in outputs] == lengths
-    assert checked[0] == sum(lengths)
+    assert counts["checked"] == sum(lengths) and counts["logprobs"] == 28
+
+
+def test_penalised_requests_through_preemption_and_reused_slots(model_folders):
+    """Six requests with penalties take turns in two state slots of a pool that cannot hold two of them
+    to their ends: a slot's bitmap is cleared for its next request, and a request that was sent back
+    has everything it holds marked again when it is computed again (portions of 24 tokens)."""
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    config, _ = P.read_model_folder(model_folders["D"])
+    prompts = prompts_for(config, [40, 33, 9, 50, 21, 5], seed=4)
+    penalties = [1.6, 1.2, 2.0, 1.0, 1.4, 0.8]
+    sampling = [SamplingParams(max_tokens=30, ignore_eos=True, temperature=0.0 if i % 2 == 0 else 0.8, seed=i,
+                               repetition_penalty=pen, logprobs=i % 3 == 0) for i, pen in enumerate(penalties)]
+    engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="bfloat16", seed=5, scheduler=SchedulerConfig(
+        max_num_seqs=2, max_num_batched_tokens=24, block_size=8, num_blocks=14)))
+    counts = check_sampling_against_the_plain_sampler(engine)
+    with engine:
+        outputs = engine.generate(prompts, sampling)
+        stats = engine.stats()
+        engine.scheduler.check_invariants()
+    assert stats["num_preemptions"] > 0 and counts["in_graph"] > 40 and stats["num_overlapped_steps"] > 20
+    assert [o.output_tokens for o in outputs] == [30] * 6 and counts["checked"] == 180 and counts["logprobs"] == 60
 
 
 def test_long_decoding_through_many_pages_and_a_window(model_folders):

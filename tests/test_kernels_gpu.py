@@ -902,6 +902,93 @@ def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row
         assert tokens[r].item() == expect
 
 
+@pytest.mark.parametrize("vocab, chunks", [(777, 8), (152064, 8), (1000, 1)])
+def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(vocab, chunks):
+    """By slot the history of a request is a bitmap over the vocabulary: ``mark_seen`` sets the bits of
+    a step's tokens for the slots that have a penalty (and for no other), the sampling kernel adds
+    the token the request ran in this step, and the ids and log-probabilities equal those of
+    ``sample`` given the same histories as lists. The tokens are chosen so that the penalty
+    decides: the largest logits of every row are in its history."""
+    from turboserve_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(vocab + 1)
+    num_slots, rows = 10, 7
+    logits = (torch.randn(rows, vocab, generator=gen) * 3).to(DEV)
+    # per slot: temperature, top_k, top_p, penalty, wants a log-probability, seed, prompt length
+    slot_opts = {4: (0.0, 0, 1.0, 1.5, 1, 1, 3), 1: (0.9, 0, 1.0, 1.3, 0, 7, 2), 8: (1.1, 30, 0.9, 2.0, 0, 9, 5),
+                 2: (0.7, 0, 0.8, 1.2, 1, 4, 1), 6: (0.0, 0, 1.0, 1.0, 1, 2, 6), 0: (1.0, 50, 1.0, 1.0, 0, 3, 2),
+                 9: (0.0, 0, 1.0, 0.7, 0, 5, 4)}
+    row_slot = [4, 1, 8, 2, 6, 0, 9]
+    row_context = [9, 12, 30, 8, 20, 5, 11]
+    words = (vocab + 31) // 32
+    temperature = torch.zeros(num_slots); top_p = torch.ones(num_slots); penalty = torch.ones(num_slots)
+    top_k = torch.zeros(num_slots, dtype=torch.int32); prompt_len = torch.zeros(num_slots, dtype=torch.int32)
+    want = torch.zeros(num_slots, dtype=torch.int32); seed = torch.zeros(num_slots, dtype=torch.int64)
+    for slot, (t, k, p, pen, lp, s, plen) in slot_opts.items():
+        temperature[slot], top_k[slot], top_p[slot], penalty[slot], want[slot], seed[slot], prompt_len[slot] = t, k, p, pen, lp, s, plen
+    dev = lambda t: t.to(DEV)
+    penalty_dev = dev(penalty)
+    # histories: the top logits of the row (so the penalty moves the choice), some random ids, the edges of the vocabulary
+    histories = []
+    for r in range(rows):
+        top = logits[r].topk(6).indices.tolist()
+        histories.append(top[:4] + torch.randint(0, vocab, (20,), generator=gen).tolist() + [0, vocab - 1, 31, 32])
+    step_tokens = [h[0] for h in histories]  # the row's best token is the one its request ran in this step
+    seen = torch.zeros(num_slots, words, dtype=torch.int32, device=DEV)
+    seen[3].fill_(-1)  # a slot nobody uses: must stay as it is
+    # one step's worth of tokens, request by request, with two padding tokens in between
+    token_ids, seq_of_token = [], []
+    for r in range(rows):
+        token_ids += histories[r][1:] + [5]
+        seq_of_token += [r] * (len(histories[r]) - 1) + [-1]
+    kernels.mark_seen(dev(torch.tensor(token_ids, dtype=torch.int32)), dev(torch.tensor(seq_of_token, dtype=torch.int32)),
+                      dev(torch.tensor(row_slot, dtype=torch.int32)), penalty_dev, seen, len(token_ids), vocab)
+    marked = seen.cpu()
+    assert marked[6].abs().sum() == 0 and marked[0].abs().sum() == 0  # slots without a penalty are not marked
+    assert (marked[3] == -1).all() and marked[5].abs().sum() == 0
+    bit = lambda slot, t: (int(marked[slot, t >> 5]) >> (t & 31)) & 1
+    assert all(bit(4, t) for t in histories[0][1:]) and not bit(4, histories[0][0])
+    assert sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in marked[4]) == len(set(histories[0][1:]))
+
+    work = torch.empty(rows * vocab, device=DEV)
+    partial = torch.zeros(rows * (2 * chunks + 1), dtype=torch.int32, device=DEV)
+    tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+    logprobs = torch.full((rows,), 123.0, device=DEV)
+    kernels.sample_slots(logits, work, tokens, rows, temperature=dev(temperature), top_k=dev(top_k), top_p=dev(top_p),
+                         seed=dev(seed), prompt_len=dev(prompt_len), row_slot=dev(torch.tensor(row_slot, dtype=torch.int32)),
+                         row_seq=None, row_context=dev(torch.tensor(row_context, dtype=torch.int32)), partial=partial,
+                         chunks=chunks, penalty=penalty_dev, seen=seen, step_tokens=dev(torch.tensor(step_tokens, dtype=torch.int32)),
+                         want_logprob=dev(want), logprobs=logprobs)
+    after = seen.cpu()
+    assert (int(after[4, step_tokens[0] >> 5]) >> (step_tokens[0] & 31)) & 1  # the step's token joined the history
+    assert after[6].abs().sum() == 0 and (after[3] == -1).all()
+    opts = [slot_opts[s] for s in row_slot]
+    by_row = torch.empty(rows, dtype=torch.int32, device=DEV)
+    by_row_logprobs = torch.empty(rows, device=DEV)
+    starts = [0]
+    for h in histories:
+        starts.append(starts[-1] + len(h))
+    kernels.sample(logits, work, by_row, temperature=dev(torch.tensor([o[0] for o in opts])),
+                   top_k=dev(torch.tensor([o[1] for o in opts], dtype=torch.int32)), top_p=dev(torch.tensor([o[2] for o in opts])),
+                   penalty=dev(torch.tensor([o[3] for o in opts])), seed=dev(torch.tensor([o[5] for o in opts], dtype=torch.int64)),
+                   counter=dev(torch.tensor([c - o[6] for c, o in zip(row_context, opts)], dtype=torch.int32)),
+                   history_start=dev(torch.tensor(starts, dtype=torch.int32)),
+                   history=dev(torch.tensor([t for h in histories for t in h], dtype=torch.int32)), logprobs=by_row_logprobs)
+    assert tokens.tolist() == by_row.tolist()
+    assert int(partial.view(rows, -1)[:, 0].abs().sum()) == 0
+    for r, o in enumerate(opts):
+        expect, logprob = P.sample_token(logits[r].cpu(), temperature=o[0], top_k=o[1], top_p=o[2], repetition_penalty=o[3],
+                                         history=histories[r], seed=o[5], counter=row_context[r] - o[6])
+        assert tokens[r].item() == expect, r
+        if o[4]:
+            assert abs(logprobs[r].item() - logprob) < 1e-4
+            filtered = o[0] > 0 and (0 < o[1] < vocab or o[2] < 1.0)  # worked by a cluster: the row's sum in another order
+            assert abs(logprobs[r].item() - by_row_logprobs[r].item()) <= (1e-5 if filtered else 0.0)
+        else:
+            assert logprobs[r].item() == 123.0  # nobody asked: not written
+    assert tokens[0].item() != logits[0].argmax().item()  # the penalty decided the greedy row
+
+
 @pytest.mark.parametrize("nh, nkv, page, window", [(28, 4, 16, None), (5, 1, 8, 300), (16, 2, 64, None)])
 def test_decode_attention_over_a_work_list(nh, nkv, page, window):
     """Every request cut into parts by its own length: more parts than a short request has 64-key tiles

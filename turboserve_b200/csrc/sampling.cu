@@ -29,9 +29,16 @@
 // top_p and seed are then indexed by row_slot[row], a row whose row_seq[row] is negative is
 // padding and is skipped, and the index of the token being generated is
 // row_context[row] - prompt_len[row_slot[row]] (the request's length after the step minus its
-// prompt), so nothing on the device has to be advanced from step to step.  A slot whose
-// temperature is negative is left alone (its request wants what this path does not do: a
-// penalty over its history, a log-probability) and its row's token is not written.
+// prompt), so nothing on the device has to be advanced from step to step.
+//
+// By slot, a request's history for the repetition penalty is a bitmap over the vocabulary
+// (`seen`, seen_words 32-bit words per slot): bit t is set once token t is among the request's
+// tokens.  ts_mark_seen sets the bits of the tokens a step runs (the portions of a prompt; after
+// a preemption, of everything that is computed again), and a row sampled by slot first sets the
+// bit of the token its request ran in this very step (`step_tokens[row]`, the token sampled one
+// step before), so the bitmap holds the whole sequence when the penalty reads it and nothing
+// has to come from the host.  Whoever gives a slot to a new request clears its words first.
+// Setting a bit twice changes nothing, so every block of a row may do it on its own.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
@@ -55,6 +62,13 @@ __host__ __device__ __forceinline__ float sample_uniform(unsigned long long seed
   x ^= x >> 27; x *= 0x94D049BB133111EBull;
   x ^= x >> 31;
   return ((float)(unsigned int)(x >> 41) + 0.5f) * (1.0f / 8388608.0f);  // 23 bits: exact, in (0, 1)
+}
+
+// The CTRL rule on one logit: a token that the request has seen becomes less likely whatever its sign.
+// `seen_row` is null for a row without a penalty.
+__device__ __forceinline__ float penalised(float v, int i, float pen, const unsigned int* seen_row) {
+  if (seen_row != nullptr && ((__ldcg(&seen_row[i >> 5]) >> (i & 31)) & 1u)) v = v < 0.0f ? v * pen : v / pen;
+  return v;
 }
 
 struct ArgMax {
@@ -146,7 +160,9 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
               const int* __restrict__ history, const int* __restrict__ history_start,
               int* __restrict__ tokens, float* __restrict__ logprobs, const int* __restrict__ row_slot,
               const int* __restrict__ row_seq, const int* __restrict__ row_context,
-              const int* __restrict__ prompt_len, int* __restrict__ partial, int skip_filtered) {
+              const int* __restrict__ prompt_len, int* __restrict__ partial, int skip_filtered,
+              const int* __restrict__ want_logprob, unsigned int* __restrict__ seen, int seen_words,
+              const int* __restrict__ step_tokens) {
   pdl_wait();
   pdl_trigger();
   __shared__ ArgMax arg_scratch[33];
@@ -171,9 +187,15 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   float* w = work + (size_t)row * vocab;
   const int tid = threadIdx.x;
   const float temp = temperature ? temperature[opt] : 0.0f;
-  if (row_slot && temp < 0.0f) return;  // a slot marked "not from here": its row is sampled by another call
-  const float pen = penalty && !row_slot ? penalty[row] : 1.0f;
-  const bool need_lse = logprobs != nullptr;
+  const float pen = penalty ? penalty[opt] : 1.0f;
+  const bool need_lse = logprobs != nullptr && (want_logprob == nullptr || want_logprob[opt] != 0);
+  // by slot the history is the slot's bitmap; the token this request ran in this step joins it first
+  unsigned int* const seen_row = (row_slot && seen && pen != 1.0f) ? seen + (size_t)opt * seen_words : nullptr;
+  if (seen_row != nullptr && step_tokens != nullptr) {
+    const int t = step_tokens[row];
+    if (tid == 0 && t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
+    __syncthreads();
+  }
   const int k = top_k ? top_k[opt] : 0;
   const float p_option = top_p ? top_p[opt] : 1.0f;
   const unsigned long long sd = seed ? seed[opt] : 0ull;
@@ -181,16 +203,16 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
 
   // -- one pass is enough: greedy, or a draw without filters ----------------------------------
   const int chunks = gridDim.y;
-  const bool one_pass = pen == 1.0f && !need_lse && (temp == 0.0f || (!(k > 0 && k < vocab) && !(p_option < 1.0f)));
+  const bool one_pass = (pen == 1.0f || seen_row != nullptr) && !need_lse && (temp == 0.0f || (!(k > 0 && k < vocab) && !(p_option < 1.0f)));
   if (one_pass && partial != nullptr) {
     const int per = (vocab + chunks - 1) / chunks;
     const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
     ArgMax pick{-INFINITY, 0x7fffffff};
     if (temp == 0.0f) {
-      for (int i = lo + tid; i < hi; i += blockDim.x) pick = better(pick, ArgMax{x[i], i});
+      for (int i = lo + tid; i < hi; i += blockDim.x) pick = better(pick, ArgMax{penalised(x[i], i, pen, seen_row), i});
     } else {
       for (int i = lo + tid; i < hi; i += blockDim.x) {
-        const float v = x[i] / temp;
+        const float v = penalised(x[i], i, pen, seen_row) / temp;
         if (v == -INFINITY) continue;
         const float u = sample_uniform(sd, ctr, (unsigned int)i);
         pick = better(pick, ArgMax{v - logf(-logf(u)), i});
@@ -218,10 +240,10 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
     return;
   }
   if (blockIdx.y != 0) return;  // a row that needs more than one pass is its first block's alone
-  if (skip_filtered && row_slot && pen == 1.0f && !need_lse && temp > 0.0f) return;  // the cluster kernel that follows draws it
+  if (skip_filtered && row_slot && temp > 0.0f && ((k > 0 && k < vocab) || p_option < 1.0f)) return;  // the cluster kernel that follows draws it
 
   // -- repetition penalty ---------------------------------------------------------------
-  for (int i = tid; i < vocab; i += blockDim.x) w[i] = x[i];
+  for (int i = tid; i < vocab; i += blockDim.x) w[i] = penalised(x[i], i, pen, seen_row);
   if (pen != 1.0f && history_start) {
     __syncthreads();
     const int h0 = history_start[row], h1 = history_start[row + 1];
@@ -420,7 +442,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   if (tid == 0) {
     tokens[row] = pick.index;
     if (need_lse) {
-      float v = x[pick.index];
+      float v = penalised(x[pick.index], pick.index, pen, seen_row);
       if (pen != 1.0f && history_start) {
         const int h0 = history_start[row], h1 = history_start[row + 1];
         for (int h = h0; h < h1; ++h)
@@ -469,7 +491,9 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
                       const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
                       const int* __restrict__ prompt_len, const int* __restrict__ row_slot,
                       const int* __restrict__ row_seq, const int* __restrict__ row_context,
-                      int* __restrict__ tokens) {
+                      int* __restrict__ tokens, const float* __restrict__ penalty,
+                      const int* __restrict__ want_logprob, unsigned int* __restrict__ seen, int seen_words,
+                      const int* __restrict__ step_tokens, float* __restrict__ logprobs) {
   pdl_wait();
   extern __shared__ float w[];  // this block's part of the row: `per` values
   __shared__ ArgMax arg_scratch[33];
@@ -480,7 +504,7 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
   __shared__ unsigned int total32[256];
   __shared__ unsigned long long hist_copies[HIST_COPIES * 256];
   unsigned int* const hist_copies32 = reinterpret_cast<unsigned int*>(hist_copies);
-  __shared__ float local_max;
+  __shared__ float local_max, lse_max, lse_sum;
   __shared__ ArgMax local_best;
   __shared__ unsigned int sel_prefix, sel_remaining;
   __shared__ unsigned long long sel_above;
@@ -494,13 +518,40 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
   const float p_keep = top_p ? top_p[opt] : 1.0f;
   const bool use_k = k > 0 && k < vocab, use_p = p_keep < 1.0f;
   if (!(temp > 0.0f) || (!use_k && !use_p)) return;  // not a row for this kernel (the same in every block of the cluster)
+  const bool need_lse = logprobs != nullptr && want_logprob != nullptr && want_logprob[opt] != 0;
   const unsigned long long sd = seed ? seed[opt] : 0ull;
   const unsigned int ctr = (unsigned int)(row_context[row] - prompt_len[opt]);
+  const float pen = penalty ? penalty[opt] : 1.0f;
+  unsigned int* const seen_row = (seen && pen != 1.0f) ? seen + (size_t)opt * seen_words : nullptr;
+  if (seen_row != nullptr && step_tokens != nullptr) {
+    const int t = step_tokens[row];
+    if (tid == 0 && t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
+    __syncthreads();
+  }
 
   const int lo = min(vocab, rank * per), count = min(vocab, lo + per) - lo;
   const float* x = logits + (size_t)row * logits_stride + lo;
-  for (int i = tid; i < count; i += blockDim.x) w[i] = x[i] / temp;
+  for (int i = tid; i < count; i += blockDim.x) w[i] = penalised(x[i], lo + i, pen, seen_row) / temp;
   __syncthreads();
+
+  // log-sum-exp of the penalised row before the temperature: every block its part, parts added in rank order
+  float lse = 0.0f;
+  if (need_lse) {
+    float mx = -INFINITY;
+    for (int i = tid; i < count; i += blockDim.x) mx = fmaxf(mx, penalised(x[i], lo + i, pen, seen_row));
+    mx = block_max(mx, f_scratch);
+    if (tid == 0) lse_max = mx;
+    sample_cluster_barrier();
+    for (int r = 0; r < SAMPLE_CLUSTER; ++r) mx = fmaxf(mx, __uint_as_float(sample_remote_u32(&lse_max, r)));
+    float sum = 0.0f;
+    for (int i = tid; i < count; i += blockDim.x) sum += expf(penalised(x[i], lo + i, pen, seen_row) - mx);
+    sum = block_sum(sum, f_scratch);
+    if (tid == 0) lse_sum = sum;
+    sample_cluster_barrier();
+    float total = 0.0f;
+    for (int r = 0; r < SAMPLE_CLUSTER; ++r) total += __uint_as_float(sample_remote_u32(&lse_sum, r));
+    lse = mx + logf(total);
+  }
 
   if (use_k) {
     if (tid == 0) { sel_prefix = 0; sel_remaining = (unsigned int)k; }
@@ -624,6 +675,7 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
     for (int r = 0; r < SAMPLE_CLUSTER; ++r)
       all = better(all, ArgMax{__uint_as_float(sample_remote_u32(&local_best.value, r)), (int)sample_remote_u32(&local_best.index, r)});
     tokens[row] = all.index;
+    if (need_lse) logprobs[row] = penalised(logits[(size_t)row * logits_stride + all.index], all.index, pen, seen_row) - lse;
   }
   sample_cluster_barrier();  // nobody leaves while its shared memory may still be read
 }
@@ -639,7 +691,8 @@ TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* wor
   if (work == nullptr || tokens == nullptr) return TS_ERR_ARGUMENT;
   ts_launch(sample_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
             temperature, top_k, top_p, penalty, seed, counter, history, history_start, tokens, logprobs,
-            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr, 0);
+            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr, 0,
+            (const int*)nullptr, (unsigned int*)nullptr, 0, (const int*)nullptr);
   return ts_launch_status();
 }
 
@@ -649,33 +702,70 @@ TS_EXPORT long long ts_sample_partial_words(int num_rows, int chunks) {
 }
 
 // The same with the options looked up by state slot (see the head of this file): temperature,
-// top_k, top_p, seed and prompt_len are arrays over the slots, row_slot / row_seq / row_context
-// are per row, `partial` is zeroed scratch of ts_sample_partial_words(num_rows, chunks) words
-// that the kernel leaves zeroed where it matters, chunks >= 1.  No penalty, no log-probabilities.
+// top_k, top_p, seed and prompt_len are arrays over the slots, and so are penalty and
+// want_logprob if given; row_slot / row_seq / row_context are per row, `partial` is zeroed
+// scratch of ts_sample_partial_words(num_rows, chunks) words that the kernel leaves zeroed where
+// it matters, chunks >= 1.  A penalty other than 1 needs `seen` (seen_words words per slot) and
+// reads `step_tokens` (per row: the token the request ran in this step) if given.  A row whose
+// slot wants a log-probability gets it in logprobs[row] (worked by one block if it needs no filter).
 TS_EXPORT int ts_sample_slots(const float* logits, long long logits_stride, float* work, int num_rows,
                               int vocab, const float* temperature, const int* top_k, const float* top_p,
                               const unsigned long long* seed, const int* prompt_len, const int* row_slot,
                               const int* row_seq, const int* row_context, int* tokens, int* partial,
-                              int chunks, cudaStream_t stream) {
+                              int chunks, const float* penalty, const int* want_logprob,
+                              unsigned int* seen, int seen_words, const int* step_tokens, float* logprobs,
+                              cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (vocab < 1 || chunks < 1 || chunks > 64) return TS_ERR_SIZE;
   if (work == nullptr || tokens == nullptr || row_slot == nullptr || row_context == nullptr || prompt_len == nullptr ||
       temperature == nullptr || partial == nullptr)
     return TS_ERR_ARGUMENT;
+  if (penalty != nullptr && (seen == nullptr || seen_words < (vocab + 31) / 32)) return TS_ERR_ARGUMENT;
+  if ((want_logprob != nullptr) != (logprobs != nullptr)) return TS_ERR_ARGUMENT;
   // rows with top-k or top-p go to a cluster of blocks that holds the row in shared memory, when it fits there
   const int per = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + 3) / 4 * 4;
   const size_t cluster_smem = (size_t)per * sizeof(float);
   const bool clustered = (top_k != nullptr || top_p != nullptr) && cluster_smem <= 180 * 1024 && num_rows <= 65535;
   ts_launch(sample_kernel, dim3(num_rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
-            temperature, top_k, top_p, (const float*)nullptr, seed, (const unsigned int*)nullptr, (const int*)nullptr,
-            (const int*)nullptr, tokens, (float*)nullptr, row_slot, row_seq, row_context, prompt_len, partial,
-            clustered ? 1 : 0);
+            temperature, top_k, top_p, penalty, seed, (const unsigned int*)nullptr, (const int*)nullptr,
+            (const int*)nullptr, tokens, logprobs, row_slot, row_seq, row_context, prompt_len, partial,
+            clustered ? 1 : 0, want_logprob, seen, seen_words, step_tokens);
   int code = ts_launch_status();
   if (code || !clustered) return code;
   cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cluster_smem);
   ts_launch_cluster(sample_cluster_kernel, dim3(SAMPLE_CLUSTER, num_rows), dim3(SAMPLE_THREADS), cluster_smem, stream,
                     SAMPLE_CLUSTER, logits, logits_stride, vocab, per, temperature, top_k, top_p, seed, prompt_len, row_slot,
-                    row_seq, row_context, tokens);
+                    row_seq, row_context, tokens, penalty, want_logprob, seen, seen_words, step_tokens, logprobs);
+  return ts_launch_status();
+}
+
+// Sets, for every token of a step whose request has a penalty other than 1, the token's bit in
+// the bitmap of the request's slot: token_ids / seq_of_token per token (a negative request is
+// padding), state_slots per request, penalty per slot.
+__global__ void mark_seen_kernel(const int* __restrict__ token_ids, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ state_slots, const float* __restrict__ penalty,
+                                 unsigned int* __restrict__ seen, int seen_words, int num_tokens, int vocab) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= num_tokens) return;
+  const int seq = seq_of_token[t];
+  if (seq < 0) return;
+  const int slot = state_slots[seq];
+  const int id = token_ids[t];
+  if (slot < 0 || penalty[slot] == 1.0f || id < 0 || id >= vocab) return;
+  atomicOr(&seen[(size_t)slot * seen_words + (id >> 5)], 1u << (id & 31));
+}
+
+TS_EXPORT int ts_mark_seen(const int* token_ids, const int* seq_of_token, const int* state_slots,
+                           const float* penalty, unsigned int* seen, int seen_words, int num_tokens,
+                           int vocab, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (token_ids == nullptr || seq_of_token == nullptr || state_slots == nullptr || penalty == nullptr || seen == nullptr)
+    return TS_ERR_ARGUMENT;
+  if (seen_words < (vocab + 31) / 32) return TS_ERR_SIZE;
+  ts_launch(mark_seen_kernel, dim3((num_tokens + 255) / 256), dim3(256), 0, stream, token_ids, seq_of_token, state_slots,
+            penalty, seen, seen_words, num_tokens, vocab);
   return ts_launch_status();
 }
 

@@ -29,16 +29,22 @@ from .sequence import Sequence
 class _Flight:
     """A step that has been launched: its plan, and how to get at the ids it samples."""
 
-    def __init__(self, plan: SchedulerOutput, rows, read, logprobs, ids: list[int] | None = None) -> None:
+    def __init__(self, plan: SchedulerOutput, rows, read, logprobs, ids: list[int] | None = None,
+                 logprobs_in_read: bool = False, in_graph: bool = False) -> None:
         self.plan, self.rows, self.read, self.logprobs, self.ids = plan, rows, read, logprobs, ids
+        self.logprobs_in_read = logprobs_in_read  # the step sampled itself: log-probabilities come with the ids
+        self.in_graph = in_graph  # sampled by the replayed graph, from the options and histories on the device
 
     def result(self) -> SamplerOutput | None:
         if self.rows is None:
             return None
         ids = self.read.finish() if self.read is not None else self.ids
-        if self.logprobs is None:
+        if self.logprobs_in_read:
+            values = self.read.logprobs()
+        elif self.logprobs is not None:
+            values = self.logprobs.tolist()
+        else:
             return SamplerOutput(ids)
-        values = self.logprobs.tolist()
         return SamplerOutput(ids, [v if r.params.logprobs else float("nan") for v, r in zip(values, self.rows)])
 
 
@@ -89,7 +95,7 @@ class LLMEngine:
             if hasattr(self.sampler, "use_slots") and (captured_with is self.sampler or not self.runner._graphs):
                 # options by state slot on the device: a captured decode step samples its own tokens
                 # as many slots as the runner has (it may have been built for more requests than this engine admits)
-                self.sampler.use_slots(max(config.scheduler.max_num_seqs, self.runner.token_buffer.numel() - 1),
+                self.sampler.use_slots(max(config.scheduler.max_num_seqs, self.runner.token_out.numel()),
                                        self.model.vocab_size)
                 self.runner.graph_sampler = self.sampler
             elif captured_with is not None:
@@ -209,8 +215,8 @@ class LLMEngine:
             return None
         for seq in flight.plan.sampling_seqs():
             params = seq.sampling
-            if params.repetition_penalty != 1.0 or params.logprobs:
-                return None  # the sampler would need the token that is still on the device / a second read
+            if (params.repetition_penalty != 1.0 or params.logprobs) and not flight.in_graph:
+                return None  # sampled from the host's copy of the history: it would need the token that is still on the device
             if seq.num_output_tokens + 1 >= params.max_tokens:
                 return None  # ends with the token that is on its way: the next step has other requests
         return self.scheduler.continue_decode(flight.plan)
@@ -224,13 +230,17 @@ class LLMEngine:
         seqs = plan.sampling_seqs()
         if not seqs:
             return _Flight(plan, None, None, None)
-        if getattr(self.runner, "sampled_in_graph", False) and all(self.sampler.fits_slots(s.sampling) for s in seqs):
-            # the replayed graph ended with the sampler, options by state slot: the ids are in token_buffer
+        if getattr(self.runner, "sampled_in_graph", False):
+            # the replayed graph ended with the sampler, options and histories by state slot: the ids
+            # (and the log-probabilities of the rows that want one) are in token_buffer
             rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending) for s in seqs]
-            return _Flight(plan, rows, self.runner.start_token_read(len(rows)), None)
+            return _Flight(plan, rows, self.runner.start_token_read(len(rows)), None,
+                           logprobs_in_read=any(s.sampling.logprobs for s in seqs), in_graph=True)
+        if ahead and any(s.sampling.repetition_penalty != 1.0 for s in seqs):
+            raise RuntimeError("a step launched ahead samples from the device's copy of the histories: it must be a replayed decode step")
         rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending,
                             s.token_ids if s.sampling.repetition_penalty != 1.0 else ()) for s in seqs]
-        tokens, logprobs = self.sampler.sample_device(logits, rows, out=self.runner.token_buffer[:-1])
+        tokens, logprobs = self.sampler.sample_device(logits, rows, out=self.runner.token_out)
         if tokens.data_ptr() == self.runner.token_buffer.data_ptr():
             return _Flight(plan, rows, self.runner.start_token_read(len(rows)), logprobs)  # tokens and the status word in one copy
         ids = tokens.tolist()

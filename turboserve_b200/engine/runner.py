@@ -63,16 +63,20 @@ def make_groups(plan: CachePlan, page_size: int, num_pages: int | Sequence[int])
 
 
 class TokenRead:
-    """A copy of the step's sampled ids (and the status word) to the host that is under way."""
+    """A copy of the step's sampled ids (with their log-probabilities and the status word) to the host that is under way."""
 
     def __init__(self, runner: "ModelRunner", host: torch.Tensor, event: torch.cuda.Event, count: int) -> None:
         self.runner, self.host, self.event, self.count = runner, host, event, count
 
     def finish(self) -> list[int]:
         self.event.synchronize()
-        values = self.host.tolist()
-        self.runner._raise_on(values[-1])
-        return values[: self.count]
+        self.runner._raise_on(int(self.host[-1]))
+        return self.host[: self.count].tolist()
+
+    def logprobs(self) -> list[float]:
+        """What the in-graph sampler left for the rows that asked for a log-probability (after :meth:`finish`)."""
+        slots = (self.host.numel() - 1) // 2
+        return self.host[slots: slots + self.count].view(torch.float32).tolist()
 
 
 class ModelRunner:
@@ -84,10 +88,13 @@ class ModelRunner:
         self.groups = groups
         self.storage = CacheStorage(self.plan, groups, num_state_slots, model.dtype, model.device)
         self.workspace = Workspace(model.device)
-        # sampled tokens and the kernels' status word share one buffer, so that the engine reads both
-        # with a single device-to-host copy: [0, num_state_slots) tokens, last element status
-        self.token_buffer = torch.zeros(num_state_slots + 1, dtype=torch.int32, device=model.device)
-        self.status = self.token_buffer[num_state_slots:]
+        # sampled tokens, their log-probabilities and the kernels' status word share one buffer, so that
+        # the engine reads all of it with a single device-to-host copy: [0, slots) tokens, [slots, 2 slots)
+        # log-probabilities (float32 bits), last element status
+        self.token_buffer = torch.zeros(2 * num_state_slots + 1, dtype=torch.int32, device=model.device)
+        self.token_out = self.token_buffer[:num_state_slots]
+        self.logprob_out = self.token_buffer[num_state_slots: 2 * num_state_slots].view(torch.float32)
+        self.status = self.token_buffer[2 * num_state_slots:]
         self._pinned: list[torch.Tensor] | None = None  # two host buffers for the ids of a step, used in turn
         self._pinned_next = 0
         self.num_steps = 0
@@ -138,6 +145,9 @@ class ModelRunner:
         batch = self.build_batch(slices)
         if device_tokens is not None:
             batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
+        if self.graph_sampler is not None:
+            # what a repetition penalty will need once these requests decode from a graph: their tokens, by slot
+            self.graph_sampler.mark_seen(batch.token_ids, batch.seq_of_token, batch.state_slots, batch.num_tokens)
         return self.run(batch)
 
     # -- decode steps from captured graphs -------------------------------------------------------
@@ -219,7 +229,8 @@ class ModelRunner:
             if self.graph_sampler is not None:
                 batch = static.batch
                 self.graph_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
-                                                  bucket, self.token_buffer[:-1])
+                                                  bucket, self.token_out, step_tokens=batch.token_ids,
+                                                  logprobs=self.logprob_out)
         entry = (graph, static, logits)
         self._graphs[(bucket, skew)] = entry
         self.num_graph_captures += 1

@@ -13,8 +13,12 @@ Per-request options also live on the device, by state slot (:class:`SlotOptions`
 written once, when a request is admitted, and a decode step finds them through the step's
 ``state_slots``; the index of the token being generated follows from the request's length, so
 nothing has to be sent or advanced per step and the sampler is part of a captured decode graph
-(:meth:`Sampler.sample_by_slot`). Rows that want a repetition penalty or log-probabilities
-still go the other way, with their options sent along.
+(:meth:`Sampler.sample_by_slot`). The history that a repetition penalty needs is there too, as
+one bit per vocabulary entry and slot: the tokens a step runs are marked by
+:meth:`Sampler.mark_seen` (portions of prompts, and everything that is computed again after a
+preemption) or by the sampling kernel itself (the one token a request ran in a decode step), so a
+penalised row needs nothing from the host either. Steps that are not replayed from a graph are
+sampled by :meth:`Sampler.sample_device`, with the options and histories sent along.
 """
 
 from __future__ import annotations
@@ -51,36 +55,53 @@ SLOT_CHUNKS = 8
 class SlotOptions:
     """Sampling options of the live requests on the device, one entry per state slot.
 
-    ``temperature``, ``top_p`` (float32), ``top_k``, ``prompt_len`` (int32) and ``seed`` (int64) are
-    arrays over the slots. A host mirror in pinned memory is changed at admission and copied
-    over whole (a few hundred bytes, on the stream, so in order with the steps around it).
+    ``temperature``, ``top_p``, ``penalty`` (float32), ``top_k``, ``prompt_len``, ``want_logprob``
+    (int32) and ``seed`` (int64) are arrays over the slots. A host mirror in pinned memory is
+    changed at admission and copied over whole (a few hundred bytes, on the stream, so in order
+    with the steps around it). ``seen`` (int32 ``[slots, ceil(vocab / 32)]``) is the bitmap of
+    the tokens each slot's request holds; the row of a slot that goes to a request with a penalty
+    is cleared by the same :meth:`flush`.
     """
 
-    def __init__(self, num_slots: int, device: torch.device) -> None:
-        self.num_slots = int(num_slots)
+    def __init__(self, num_slots: int, vocab: int, device: torch.device) -> None:
+        self.num_slots, self.vocab = int(num_slots), int(vocab)
+        n = self.num_slots
         pin = device.type == "cuda"
-        self._host_f = torch.zeros(2 * num_slots, dtype=torch.float32)
-        self._host_i = torch.zeros(2 * num_slots, dtype=torch.int32)
-        self._host_s = torch.zeros(num_slots, dtype=torch.int64)
+        self._host_f = torch.zeros(3 * n, dtype=torch.float32)
+        self._host_i = torch.zeros(3 * n, dtype=torch.int32)
+        self._host_s = torch.zeros(n, dtype=torch.int64)
         if pin:
             self._host_f, self._host_i, self._host_s = self._host_f.pin_memory(), self._host_i.pin_memory(), self._host_s.pin_memory()
-        self._host_f[num_slots:] = 1.0  # top_p
+        self._host_f[n:] = 1.0  # top_p, penalty
         self._dev_f = self._host_f.to(device)
         self._dev_i = self._host_i.to(device)
         self.seed = self._host_s.to(device)
-        self.temperature, self.top_p = self._dev_f[:num_slots], self._dev_f[num_slots:]
-        self.top_k, self.prompt_len = self._dev_i[:num_slots], self._dev_i[num_slots:]
+        self.temperature, self.top_p, self.penalty = self._dev_f[:n], self._dev_f[n:2 * n], self._dev_f[2 * n:]
+        self.top_k, self.prompt_len, self.want_logprob = self._dev_i[:n], self._dev_i[n:2 * n], self._dev_i[2 * n:]
+        self.seen = torch.zeros(n, (self.vocab + 31) // 32, dtype=torch.int32, device=device)
         self._dirty = False
+        self._to_clear: list[int] = []
+        self._penalised: set[int] = set()
+
+    @property
+    def any_penalty(self) -> bool:
+        """Whether any slot holds a request with a penalty (only then do a step's tokens have to be marked)."""
+        return bool(self._penalised)
 
     def set(self, slot: int, params: SamplingParams, seed: int, num_prompt_tokens: int) -> None:
         n = self.num_slots
-        # a request that needs its history or a log-probability is sampled with its options sent along;
-        # a negative temperature tells the kernel that reads these arrays to leave its row alone
-        self._host_f[slot] = params.temperature if Sampler.fits_slots(params) else -1.0
+        self._host_f[slot] = params.temperature
         self._host_f[n + slot] = params.top_p
+        self._host_f[2 * n + slot] = params.repetition_penalty
         self._host_i[slot] = params.top_k
         self._host_i[n + slot] = num_prompt_tokens
+        self._host_i[2 * n + slot] = 1 if params.logprobs else 0
         self._host_s[slot] = seed & 0x7FFFFFFFFFFFFFFF
+        if params.repetition_penalty != 1.0:
+            self._to_clear.append(slot)  # what the slot's last request had seen is not this one's
+            self._penalised.add(slot)
+        else:
+            self._penalised.discard(slot)
         self._dirty = True
 
     def flush(self) -> None:
@@ -89,6 +110,9 @@ class SlotOptions:
             self._dev_f.copy_(self._host_f, non_blocking=True)
             self._dev_i.copy_(self._host_i, non_blocking=True)
             self.seed.copy_(self._host_s, non_blocking=True)
+            for slot in self._to_clear:
+                self.seen[slot].zero_()
+            self._to_clear.clear()
             self._dirty = False
 
 
@@ -102,29 +126,38 @@ class Sampler:
     def use_slots(self, num_slots: int, vocab: int) -> SlotOptions:
         """Keep per-request options on the device for up to ``num_slots`` requests; sizes the scratch
         of :meth:`sample_by_slot` once, so that it can be part of a captured graph."""
-        if self.slots is None or self.slots.num_slots < num_slots:
-            self.slots = SlotOptions(num_slots, self.device)
+        if self.slots is None or self.slots.num_slots < num_slots or self.slots.vocab != vocab:
+            self.slots = SlotOptions(num_slots, vocab, self.device)
             self._partial = torch.zeros(num_slots * (2 * SLOT_CHUNKS + 1), dtype=torch.int32, device=self.device)
         self._scratch(num_slots, vocab)
         return self.slots
 
-    @staticmethod
-    def fits_slots(params: SamplingParams) -> bool:
-        """Whether a row with these options can be sampled from the slot arrays (no penalty, no log-probabilities)."""
-        return params.repetition_penalty == 1.0 and not params.logprobs
-
     def sample_by_slot(self, logits: torch.Tensor, row_slot: torch.Tensor, row_seq: torch.Tensor | None,
-                       row_context: torch.Tensor, num_rows: int, out: torch.Tensor) -> torch.Tensor:
-        """Sample ``num_rows`` rows whose options are in :attr:`slots`; ids into ``out``. Allocates nothing."""
+                       row_context: torch.Tensor, num_rows: int, out: torch.Tensor,
+                       step_tokens: torch.Tensor | None = None, logprobs: torch.Tensor | None = None) -> torch.Tensor:
+        """Sample ``num_rows`` rows whose options are in :attr:`slots`; ids into ``out``. Allocates nothing.
+
+        ``step_tokens`` (per row: the token the row's request ran in this step) joins the request's
+        history before a penalty reads it; without it the history is what :meth:`mark_seen` has
+        marked. ``logprobs`` (float32 per row) takes the log-probability of the chosen token for
+        the rows whose request asked for it; without it nobody gets one.
+        """
         if self.slots is None or self._partial is None:
             raise RuntimeError("use_slots() first")
         slots = self.slots
         kernels.sample_slots(
             logits, self._scratch(num_rows, logits.shape[1]), out, num_rows, temperature=slots.temperature, top_k=slots.top_k,
             top_p=slots.top_p, seed=slots.seed, prompt_len=slots.prompt_len, row_slot=row_slot, row_seq=row_seq,
-            row_context=row_context, partial=self._partial, chunks=SLOT_CHUNKS,
+            row_context=row_context, partial=self._partial, chunks=SLOT_CHUNKS, penalty=slots.penalty, seen=slots.seen,
+            step_tokens=step_tokens, want_logprob=slots.want_logprob if logprobs is not None else None, logprobs=logprobs,
         )
         return out[:num_rows]
+
+    def mark_seen(self, token_ids: torch.Tensor, seq_of_token: torch.Tensor, state_slots: torch.Tensor, num_tokens: int) -> None:
+        """Add a step's tokens to the histories of the requests that have a penalty (a kernel, nothing if no slot has one)."""
+        if self.slots is None or not self.slots.any_penalty:
+            return
+        kernels.mark_seen(token_ids, seq_of_token, state_slots, self.slots.penalty, self.slots.seen, num_tokens, self.slots.vocab)
 
     def _scratch(self, rows: int, vocab: int) -> torch.Tensor:
         need = rows * vocab
