@@ -28,7 +28,7 @@ class HostRunner:
         self.fail_reads = 0
         self.steps = []
 
-    def step(self, slices, device_tokens=None):
+    def step(self, slices, device_tokens=None, sample=False):
         self.steps.append([(len(piece.token_ids), piece.start_position) for piece in slices])
         rows = sum(len(piece.want) for piece in slices)
         logits = torch.zeros(rows, 32)

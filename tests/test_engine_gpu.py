@@ -138,14 +138,14 @@ def test_temperature_sampling_matches_the_plain_sampler(model_folders, name):
 def check_sampling_against_the_plain_sampler(engine):
     """Hook an engine so that every sampled id (and log-probability) is compared with what the plain
     sampler draws from the very row of logits the step produced. Returns the counters
-    ``{"checked", "in_graph", "logprobs"}``, which go up as the engine runs."""
-    launched, counts = [], {"checked": 0, "in_graph": 0, "logprobs": 0}
+    ``{"checked", "in_step", "logprobs"}``, which go up as the engine runs."""
+    launched, counts = [], {"checked": 0, "in_step": 0, "logprobs": 0}
     run_step, process = engine.runner.step, engine._process
 
-    def recording_step(slices, device_tokens=None):
-        logits = run_step(slices, device_tokens)
+    def recording_step(slices, device_tokens=None, sample=False):
+        logits = run_step(slices, device_tokens, sample)
         launched.append(None if logits is None else logits.clone())
-        counts["in_graph"] += int(engine.runner.sampled_in_graph)
+        counts["in_step"] += int(engine.runner.sampled_in_step)
         return logits
 
     def checking_process(plan, result):
@@ -186,12 +186,12 @@ def test_bfloat16_sampled_rows_match_the_plain_sampler_on_the_engines_own_logits
         max_num_seqs=8, max_num_batched_tokens=256, block_size=16, num_blocks=64)))
     counts = check_sampling_against_the_plain_sampler(engine)
     with engine:
-        assert engine.runner.graph_sampler is engine.sampler and engine.sampler.slots is not None
+        assert engine.runner.step_sampler is engine.sampler and engine.sampler.slots is not None
         lengths = [14, 14, 14, 14, 14]
         outputs = engine.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True, **o) for n, o in zip(lengths, options)])
         stats = engine.stats()
-        # every decode step sampled itself, and all but the first were launched ahead of the ids before them
-        assert counts["in_graph"] == 13 and stats["num_overlapped_steps"] >= 10 and engine.runner.num_graph_replays == 13
+        # every step sampled itself, and all but the first and the last were launched ahead of the ids before them
+        assert counts["in_step"] == 14 and stats["num_overlapped_steps"] >= 11 and engine.runner.num_graph_replays == 13
     assert [o.output_tokens for o in outputs] == lengths
     assert counts["checked"] == sum(lengths) and counts["logprobs"] == 28
 
@@ -214,7 +214,7 @@ def test_penalised_requests_through_preemption_and_reused_slots(model_folders):
         outputs = engine.generate(prompts, sampling)
         stats = engine.stats()
         engine.scheduler.check_invariants()
-    assert stats["num_preemptions"] > 0 and counts["in_graph"] > 40 and stats["num_overlapped_steps"] > 20
+    assert stats["num_preemptions"] > 0 and counts["in_step"] > 40 and stats["num_overlapped_steps"] > 20
     assert [o.output_tokens for o in outputs] == [30] * 6 and counts["checked"] == 180 and counts["logprobs"] == 60
 
 

@@ -882,8 +882,8 @@ def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row
     for _ in range(2):  # twice: the counters in `partial` are left at zero
         tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
         kernels.sample_slots(logits, work, tokens, rows, temperature=dev(temperature), top_k=dev(top_k), top_p=dev(top_p),
-                             seed=dev(seed), prompt_len=dev(prompt_len), row_slot=dev(torch.tensor(row_slot, dtype=torch.int32)),
-                             row_seq=dev(torch.tensor(row_seq, dtype=torch.int32)), row_context=dev(torch.tensor(row_context, dtype=torch.int32)),
+                             seed=dev(seed), prompt_len=dev(prompt_len), seq_slot=dev(torch.tensor(row_slot, dtype=torch.int32)),
+                             seq_of_token=dev(torch.tensor(row_seq, dtype=torch.int32)), seq_context=dev(torch.tensor(row_context, dtype=torch.int32)),
                              partial=partial, chunks=chunks)
         live = rows - 1
         by_row = torch.empty(live, dtype=torch.int32, device=DEV)
@@ -906,9 +906,10 @@ def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row
 def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(vocab, chunks):
     """By slot the history of a request is a bitmap over the vocabulary: ``mark_seen`` sets the bits of
     a step's tokens for the slots that have a penalty (and for no other), the sampling kernel adds
-    the token the request ran in this step, and the ids and log-probabilities equal those of
+    the token whose logits a row holds, and the ids and log-probabilities equal those of
     ``sample`` given the same histories as lists. The tokens are chosen so that the penalty
-    decides: the largest logits of every row are in its history."""
+    decides: the largest logits of every row are in its history. A row finds its request as in a
+    step with prompts in it: row -> token of the step -> request -> slot, none of them the identity."""
     from turboserve_b200.ops import kernels
 
     gen = torch.Generator().manual_seed(vocab + 1)
@@ -936,13 +937,23 @@ def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(v
     step_tokens = [h[0] for h in histories]  # the row's best token is the one its request ran in this step
     seen = torch.zeros(num_slots, words, dtype=torch.int32, device=DEV)
     seen[3].fill_(-1)  # a slot nobody uses: must stay as it is
-    # one step's worth of tokens, request by request, with two padding tokens in between
-    token_ids, seq_of_token = [], []
+    # One step's worth of tokens. The requests of the step come in the reverse order of the rows
+    # (request q's logits are row rows - 1 - q), each brings its history but for the token at its
+    # end, whose logits the row holds; mark_seen sees that last token as padding, so that only the
+    # sampling kernel can have added it.
+    token_ids, seq_of_token, last_token = [], [], {}
+    for q in range(rows):
+        r = rows - 1 - q
+        token_ids += histories[r][1:] + [histories[r][0]]
+        seq_of_token += [q] * len(histories[r])
+        last_token[r] = len(token_ids) - 1
+    seq_slot = dev(torch.tensor([row_slot[rows - 1 - q] for q in range(rows)], dtype=torch.int32))
+    seq_context = dev(torch.tensor([row_context[rows - 1 - q] for q in range(rows)], dtype=torch.int32))
+    without_last = list(seq_of_token)
     for r in range(rows):
-        token_ids += histories[r][1:] + [5]
-        seq_of_token += [r] * (len(histories[r]) - 1) + [-1]
-    kernels.mark_seen(dev(torch.tensor(token_ids, dtype=torch.int32)), dev(torch.tensor(seq_of_token, dtype=torch.int32)),
-                      dev(torch.tensor(row_slot, dtype=torch.int32)), penalty_dev, seen, len(token_ids), vocab)
+        without_last[last_token[r]] = -1
+    kernels.mark_seen(dev(torch.tensor(token_ids, dtype=torch.int32)), dev(torch.tensor(without_last, dtype=torch.int32)),
+                      seq_slot, penalty_dev, seen, len(token_ids), vocab)
     marked = seen.cpu()
     assert marked[6].abs().sum() == 0 and marked[0].abs().sum() == 0  # slots without a penalty are not marked
     assert (marked[3] == -1).all() and marked[5].abs().sum() == 0
@@ -955,9 +966,10 @@ def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(v
     tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
     logprobs = torch.full((rows,), 123.0, device=DEV)
     kernels.sample_slots(logits, work, tokens, rows, temperature=dev(temperature), top_k=dev(top_k), top_p=dev(top_p),
-                         seed=dev(seed), prompt_len=dev(prompt_len), row_slot=dev(torch.tensor(row_slot, dtype=torch.int32)),
-                         row_seq=None, row_context=dev(torch.tensor(row_context, dtype=torch.int32)), partial=partial,
-                         chunks=chunks, penalty=penalty_dev, seen=seen, step_tokens=dev(torch.tensor(step_tokens, dtype=torch.int32)),
+                         seed=dev(seed), prompt_len=dev(prompt_len), seq_slot=seq_slot, seq_context=seq_context, partial=partial,
+                         chunks=chunks, row_token=dev(torch.tensor([last_token[r] for r in range(rows)], dtype=torch.int32)),
+                         seq_of_token=dev(torch.tensor(seq_of_token, dtype=torch.int32)),
+                         step_tokens=dev(torch.tensor(token_ids, dtype=torch.int32)), penalty=penalty_dev, seen=seen,
                          want_logprob=dev(want), logprobs=logprobs)
     after = seen.cpu()
     assert (int(after[4, step_tokens[0] >> 5]) >> (step_tokens[0] & 31)) & 1  # the step's token joined the history

@@ -25,18 +25,21 @@
 // the filters is worked by its first block alone.  `partial` holds rows * (2 * chunks + 1) words
 // and its counters must be zero before the first call; the kernel leaves them zero.
 //
-// Options may also be looked up by state slot (row_slot != null): the arrays temperature, top_k,
-// top_p and seed are then indexed by row_slot[row], a row whose row_seq[row] is negative is
-// padding and is skipped, and the index of the token being generated is
-// row_context[row] - prompt_len[row_slot[row]] (the request's length after the step minus its
-// prompt), so nothing on the device has to be advanced from step to step.
+// Options may also be looked up by state slot (RowLookup, filled from a step's own index arrays):
+// row -> the step's token whose logits it holds (row_token, or the row itself) -> that token's
+// request in the step (seq_of_token, or the token itself; negative: padding, the row is skipped)
+// -> the request's state slot (seq_slot) and its length after the step (seq_context).  The
+// arrays temperature, top_k, top_p, penalty, want_logprob, seed and prompt_len are then indexed
+// by the slot, and the index of the token being generated is seq_context - prompt_len[slot] (the
+// request's length after the step minus its prompt), so nothing on the device has to be
+// advanced from step to step.
 //
 // By slot, a request's history for the repetition penalty is a bitmap over the vocabulary
 // (`seen`, seen_words 32-bit words per slot): bit t is set once token t is among the request's
 // tokens.  ts_mark_seen sets the bits of the tokens a step runs (the portions of a prompt; after
 // a preemption, of everything that is computed again), and a row sampled by slot first sets the
-// bit of the token its request ran in this very step (`step_tokens[row]`, the token sampled one
-// step before), so the bitmap holds the whole sequence when the penalty reads it and nothing
+// bit of the token its logits come from (`step_tokens`, per token of the step: in a decode step
+// the token sampled one step before), so the bitmap holds the whole sequence when the penalty reads it and nothing
 // has to come from the host.  Whoever gives a slot to a new request clears its words first.
 // Setting a bit twice changes nothing, so every block of a row may do it on its own.
 #include "common.cuh"
@@ -70,6 +73,15 @@ __device__ __forceinline__ float penalised(float v, int i, float pen, const unsi
   if (seen_row != nullptr && ((__ldcg(&seen_row[i >> 5]) >> (i & 31)) & 1u)) v = v < 0.0f ? v * pen : v / pen;
   return v;
 }
+
+// How a row finds its request in the index arrays of a step (see the head of this file).
+struct RowLookup {
+  const int* row_token;     // per row, or null: token = row
+  const int* seq_of_token;  // per token, or null: request = token
+  const int* seq_slot;      // per request; null: options are per row, not by slot
+  const int* seq_context;   // per request
+  const int* step_tokens;   // per token, or null
+};
 
 struct ArgMax {
   float value;
@@ -158,11 +170,9 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
               const float* __restrict__ top_p, const float* __restrict__ penalty,
               const unsigned long long* __restrict__ seed, const unsigned int* __restrict__ counter,
               const int* __restrict__ history, const int* __restrict__ history_start,
-              int* __restrict__ tokens, float* __restrict__ logprobs, const int* __restrict__ row_slot,
-              const int* __restrict__ row_seq, const int* __restrict__ row_context,
+              int* __restrict__ tokens, float* __restrict__ logprobs, const RowLookup look,
               const int* __restrict__ prompt_len, int* __restrict__ partial, int skip_filtered,
-              const int* __restrict__ want_logprob, unsigned int* __restrict__ seen, int seen_words,
-              const int* __restrict__ step_tokens) {
+              const int* __restrict__ want_logprob, unsigned int* __restrict__ seen, int seen_words) {
   pdl_wait();
   pdl_trigger();
   __shared__ ArgMax arg_scratch[33];
@@ -181,8 +191,14 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   __shared__ unsigned int sel_remaining;
 
   const int row = blockIdx.x;
-  if (row_seq && row_seq[row] < 0) return;  // a padding row of a fixed-size batch
-  const int opt = row_slot ? row_slot[row] : row;  // where this row's options are
+  const bool by_slot = look.seq_slot != nullptr;
+  int step_token = row, seq = row;
+  if (by_slot) {
+    step_token = look.row_token ? look.row_token[row] : row;
+    seq = look.seq_of_token ? look.seq_of_token[step_token] : step_token;
+    if (seq < 0) return;  // a padding row of a fixed-size batch
+  }
+  const int opt = by_slot ? look.seq_slot[seq] : row;  // where this row's options are
   const float* x = logits + (size_t)row * logits_stride;
   float* w = work + (size_t)row * vocab;
   const int tid = threadIdx.x;
@@ -190,16 +206,16 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
   const float pen = penalty ? penalty[opt] : 1.0f;
   const bool need_lse = logprobs != nullptr && (want_logprob == nullptr || want_logprob[opt] != 0);
   // by slot the history is the slot's bitmap; the token this request ran in this step joins it first
-  unsigned int* const seen_row = (row_slot && seen && pen != 1.0f) ? seen + (size_t)opt * seen_words : nullptr;
-  if (seen_row != nullptr && step_tokens != nullptr) {
-    const int t = step_tokens[row];
+  unsigned int* const seen_row = (by_slot && seen && pen != 1.0f) ? seen + (size_t)opt * seen_words : nullptr;
+  if (seen_row != nullptr && look.step_tokens != nullptr) {
+    const int t = look.step_tokens[step_token];
     if (tid == 0 && t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
     __syncthreads();
   }
   const int k = top_k ? top_k[opt] : 0;
   const float p_option = top_p ? top_p[opt] : 1.0f;
   const unsigned long long sd = seed ? seed[opt] : 0ull;
-  const unsigned int ctr = row_slot ? (unsigned int)(row_context[row] - prompt_len[opt]) : (counter ? counter[row] : 0u);
+  const unsigned int ctr = by_slot ? (unsigned int)(look.seq_context[seq] - prompt_len[opt]) : (counter ? counter[row] : 0u);
 
   // -- one pass is enough: greedy, or a draw without filters ----------------------------------
   const int chunks = gridDim.y;
@@ -240,7 +256,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
     return;
   }
   if (blockIdx.y != 0) return;  // a row that needs more than one pass is its first block's alone
-  if (skip_filtered && row_slot && temp > 0.0f && ((k > 0 && k < vocab) || p_option < 1.0f)) return;  // the cluster kernel that follows draws it
+  if (skip_filtered && by_slot && temp > 0.0f && ((k > 0 && k < vocab) || p_option < 1.0f)) return;  // the cluster kernel that follows draws it
 
   // -- repetition penalty ---------------------------------------------------------------
   for (int i = tid; i < vocab; i += blockDim.x) w[i] = penalised(x[i], i, pen, seen_row);
@@ -489,11 +505,10 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride, int vocab, int per,
                       const float* __restrict__ temperature, const int* __restrict__ top_k,
                       const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
-                      const int* __restrict__ prompt_len, const int* __restrict__ row_slot,
-                      const int* __restrict__ row_seq, const int* __restrict__ row_context,
+                      const int* __restrict__ prompt_len, const RowLookup look,
                       int* __restrict__ tokens, const float* __restrict__ penalty,
                       const int* __restrict__ want_logprob, unsigned int* __restrict__ seen, int seen_words,
-                      const int* __restrict__ step_tokens, float* __restrict__ logprobs) {
+                      float* __restrict__ logprobs) {
   pdl_wait();
   extern __shared__ float w[];  // this block's part of the row: `per` values
   __shared__ ArgMax arg_scratch[33];
@@ -511,8 +526,10 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
 
   const int row = blockIdx.y, rank = blockIdx.x, tid = threadIdx.x;  // the cluster lies along x
   const int copy = tid & (HIST_COPIES - 1);
-  if (row_seq && row_seq[row] < 0) return;
-  const int opt = row_slot[row];
+  const int step_token = look.row_token ? look.row_token[row] : row;
+  const int seq = look.seq_of_token ? look.seq_of_token[step_token] : step_token;
+  if (seq < 0) return;
+  const int opt = look.seq_slot[seq];
   const float temp = temperature[opt];
   const int k = top_k ? top_k[opt] : 0;
   const float p_keep = top_p ? top_p[opt] : 1.0f;
@@ -520,11 +537,11 @@ sample_cluster_kernel(const float* __restrict__ logits, long long logits_stride,
   if (!(temp > 0.0f) || (!use_k && !use_p)) return;  // not a row for this kernel (the same in every block of the cluster)
   const bool need_lse = logprobs != nullptr && want_logprob != nullptr && want_logprob[opt] != 0;
   const unsigned long long sd = seed ? seed[opt] : 0ull;
-  const unsigned int ctr = (unsigned int)(row_context[row] - prompt_len[opt]);
+  const unsigned int ctr = (unsigned int)(look.seq_context[seq] - prompt_len[opt]);
   const float pen = penalty ? penalty[opt] : 1.0f;
   unsigned int* const seen_row = (seen && pen != 1.0f) ? seen + (size_t)opt * seen_words : nullptr;
-  if (seen_row != nullptr && step_tokens != nullptr) {
-    const int t = step_tokens[row];
+  if (seen_row != nullptr && look.step_tokens != nullptr) {
+    const int t = look.step_tokens[step_token];
     if (tid == 0 && t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
     __syncthreads();
   }
@@ -691,8 +708,8 @@ TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* wor
   if (work == nullptr || tokens == nullptr) return TS_ERR_ARGUMENT;
   ts_launch(sample_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
             temperature, top_k, top_p, penalty, seed, counter, history, history_start, tokens, logprobs,
-            (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (const int*)nullptr, (int*)nullptr, 0,
-            (const int*)nullptr, (unsigned int*)nullptr, 0, (const int*)nullptr);
+            RowLookup{nullptr, nullptr, nullptr, nullptr, nullptr}, (const int*)nullptr, (int*)nullptr, 0,
+            (const int*)nullptr, (unsigned int*)nullptr, 0);
   return ts_launch_status();
 }
 
@@ -703,39 +720,41 @@ TS_EXPORT long long ts_sample_partial_words(int num_rows, int chunks) {
 
 // The same with the options looked up by state slot (see the head of this file): temperature,
 // top_k, top_p, seed and prompt_len are arrays over the slots, and so are penalty and
-// want_logprob if given; row_slot / row_seq / row_context are per row, `partial` is zeroed
-// scratch of ts_sample_partial_words(num_rows, chunks) words that the kernel leaves zeroed where
-// it matters, chunks >= 1.  A penalty other than 1 needs `seen` (seen_words words per slot) and
-// reads `step_tokens` (per row: the token the request ran in this step) if given.  A row whose
-// slot wants a log-probability gets it in logprobs[row] (worked by one block if it needs no filter).
+// want_logprob if given; row_token, seq_of_token, seq_slot, seq_context and step_tokens are the
+// step's index arrays (RowLookup); `partial` is zeroed scratch of
+// ts_sample_partial_words(num_rows, chunks) words that the kernel leaves zeroed where it
+// matters, chunks >= 1.  A penalty other than 1 needs `seen` (seen_words words per slot).  A row
+// whose slot wants a log-probability gets it in logprobs[row] (worked by one block if it needs
+// no filter).
 TS_EXPORT int ts_sample_slots(const float* logits, long long logits_stride, float* work, int num_rows,
                               int vocab, const float* temperature, const int* top_k, const float* top_p,
-                              const unsigned long long* seed, const int* prompt_len, const int* row_slot,
-                              const int* row_seq, const int* row_context, int* tokens, int* partial,
-                              int chunks, const float* penalty, const int* want_logprob,
-                              unsigned int* seen, int seen_words, const int* step_tokens, float* logprobs,
-                              cudaStream_t stream) {
+                              const unsigned long long* seed, const int* prompt_len, const int* row_token,
+                              const int* seq_of_token, const int* seq_slot, const int* seq_context,
+                              const int* step_tokens, int* tokens, int* partial, int chunks,
+                              const float* penalty, const int* want_logprob, unsigned int* seen,
+                              int seen_words, float* logprobs, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (vocab < 1 || chunks < 1 || chunks > 64) return TS_ERR_SIZE;
-  if (work == nullptr || tokens == nullptr || row_slot == nullptr || row_context == nullptr || prompt_len == nullptr ||
+  if (work == nullptr || tokens == nullptr || seq_slot == nullptr || seq_context == nullptr || prompt_len == nullptr ||
       temperature == nullptr || partial == nullptr)
     return TS_ERR_ARGUMENT;
   if (penalty != nullptr && (seen == nullptr || seen_words < (vocab + 31) / 32)) return TS_ERR_ARGUMENT;
   if ((want_logprob != nullptr) != (logprobs != nullptr)) return TS_ERR_ARGUMENT;
+  const RowLookup look{row_token, seq_of_token, seq_slot, seq_context, step_tokens};
   // rows with top-k or top-p go to a cluster of blocks that holds the row in shared memory, when it fits there
   const int per = ((vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER + 3) / 4 * 4;
   const size_t cluster_smem = (size_t)per * sizeof(float);
   const bool clustered = (top_k != nullptr || top_p != nullptr) && cluster_smem <= 180 * 1024 && num_rows <= 65535;
   ts_launch(sample_kernel, dim3(num_rows, chunks), dim3(SAMPLE_THREADS), 0, stream, logits, logits_stride, work, vocab,
             temperature, top_k, top_p, penalty, seed, (const unsigned int*)nullptr, (const int*)nullptr,
-            (const int*)nullptr, tokens, logprobs, row_slot, row_seq, row_context, prompt_len, partial,
-            clustered ? 1 : 0, want_logprob, seen, seen_words, step_tokens);
+            (const int*)nullptr, tokens, logprobs, look, prompt_len, partial, clustered ? 1 : 0, want_logprob, seen,
+            seen_words);
   int code = ts_launch_status();
   if (code || !clustered) return code;
   cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cluster_smem);
   ts_launch_cluster(sample_cluster_kernel, dim3(SAMPLE_CLUSTER, num_rows), dim3(SAMPLE_THREADS), cluster_smem, stream,
-                    SAMPLE_CLUSTER, logits, logits_stride, vocab, per, temperature, top_k, top_p, seed, prompt_len, row_slot,
-                    row_seq, row_context, tokens, penalty, want_logprob, seen, seen_words, step_tokens, logprobs);
+                    SAMPLE_CLUSTER, logits, logits_stride, vocab, per, temperature, top_k, top_p, seed, prompt_len, look,
+                    tokens, penalty, want_logprob, seen, seen_words, logprobs);
   return ts_launch_status();
 }
 

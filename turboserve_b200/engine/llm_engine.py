@@ -30,10 +30,10 @@ class _Flight:
     """A step that has been launched: its plan, and how to get at the ids it samples."""
 
     def __init__(self, plan: SchedulerOutput, rows, read, logprobs, ids: list[int] | None = None,
-                 logprobs_in_read: bool = False, in_graph: bool = False) -> None:
+                 logprobs_in_read: bool = False, in_step: bool = False) -> None:
         self.plan, self.rows, self.read, self.logprobs, self.ids = plan, rows, read, logprobs, ids
         self.logprobs_in_read = logprobs_in_read  # the step sampled itself: log-probabilities come with the ids
-        self.in_graph = in_graph  # sampled by the replayed graph, from the options and histories on the device
+        self.in_step = in_step  # sampled by the step itself, from the options and histories on the device
 
     def result(self) -> SamplerOutput | None:
         if self.rows is None:
@@ -79,7 +79,7 @@ class LLMEngine:
         if sampler is None:
             # a runner whose captured graphs already end with a sampler keeps that sampler: its options by
             # state slot are what those graphs read
-            sampler = getattr(runner, "graph_sampler", None) or Sampler(runner.device)
+            sampler = getattr(runner, "step_sampler", None) or Sampler(runner.device)
         self.sampler = sampler
         self._eos_token_ids = frozenset(int(t) for t in getattr(self.model.spec, "eos_token_ids", ()))
         self._seed_source = random.Random(config.seed)
@@ -90,16 +90,18 @@ class LLMEngine:
         self._generate_calls = 0
         self._in_flight: _Flight | None = None
         self._num_overlapped_steps = 0
-        if config.cuda_graphs and self.runner.dtype == torch.bfloat16 and hasattr(self.runner, "enable_graphs"):
-            captured_with = getattr(self.runner, "graph_sampler", None)
-            if hasattr(self.sampler, "use_slots") and (captured_with is self.sampler or not self.runner._graphs):
-                # options by state slot on the device: a captured decode step samples its own tokens
-                # as many slots as the runner has (it may have been built for more requests than this engine admits)
+        if hasattr(self.sampler, "use_slots") and hasattr(self.runner, "step_sampler"):
+            captured_with = self.runner.step_sampler
+            if captured_with is self.sampler or not getattr(self.runner, "_graphs", None):
+                # options and histories by state slot on the device: a step samples its own tokens (inside the
+                # captured graph where there is one); as many slots as the runner has (it may have been built
+                # for more requests than this engine admits)
                 self.sampler.use_slots(max(config.scheduler.max_num_seqs, self.runner.token_out.numel()),
                                        self.model.vocab_size)
-                self.runner.graph_sampler = self.sampler
-            elif captured_with is not None:
-                self.runner.graph_sampler = None  # graphs captured with another sampler: their ids are not used
+                self.runner.step_sampler = self.sampler
+            else:
+                self.runner.step_sampler = None  # graphs captured with another sampler: their ids are not used
+        if config.cuda_graphs and self.runner.dtype == torch.bfloat16 and hasattr(self.runner, "enable_graphs"):
             pages = min(g.num_pages for g in self.runner.groups)
             longest = min(config.max_model_len or pages * config.block_size, pages * config.block_size)
             self.runner.enable_graphs(config.scheduler.max_num_seqs, longest, config.scheduler.max_num_batched_tokens)
@@ -215,7 +217,7 @@ class LLMEngine:
             return None
         for seq in flight.plan.sampling_seqs():
             params = seq.sampling
-            if (params.repetition_penalty != 1.0 or params.logprobs) and not flight.in_graph:
+            if (params.repetition_penalty != 1.0 or params.logprobs) and not flight.in_step:
                 return None  # sampled from the host's copy of the history: it would need the token that is still on the device
             if seq.num_output_tokens + 1 >= params.max_tokens:
                 return None  # ends with the token that is on its way: the next step has other requests
@@ -226,18 +228,18 @@ class LLMEngine:
         pending = 1 if ahead else 0  # tokens of a request that are sampled but not read yet: they count for the draw's index
         if getattr(self.sampler, "slots", None) is not None:
             self.sampler.slots.flush()
-        logits = self.runner.step(plan.slices(), device_tokens=self.runner.token_buffer if ahead else None)
+        logits = self.runner.step(plan.slices(), device_tokens=self.runner.token_buffer if ahead else None, sample=True)
         seqs = plan.sampling_seqs()
         if not seqs:
             return _Flight(plan, None, None, None)
-        if getattr(self.runner, "sampled_in_graph", False):
-            # the replayed graph ended with the sampler, options and histories by state slot: the ids
-            # (and the log-probabilities of the rows that want one) are in token_buffer
+        if getattr(self.runner, "sampled_in_step", False):
+            # the step ended with the sampler, options and histories by state slot: the ids (and the
+            # log-probabilities of the rows that want one) are in token_buffer
             rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending) for s in seqs]
             return _Flight(plan, rows, self.runner.start_token_read(len(rows)), None,
-                           logprobs_in_read=any(s.sampling.logprobs for s in seqs), in_graph=True)
+                           logprobs_in_read=any(s.sampling.logprobs for s in seqs), in_step=True)
         if ahead and any(s.sampling.repetition_penalty != 1.0 for s in seqs):
-            raise RuntimeError("a step launched ahead samples from the device's copy of the histories: it must be a replayed decode step")
+            raise RuntimeError("a step launched ahead needs the histories on the device: its sampler must be the runner's step_sampler")
         rows = [SamplingRow(s.sampling, s.seed, s.num_output_tokens + pending,
                             s.token_ids if s.sampling.repetition_penalty != 1.0 else ()) for s in seqs]
         tokens, logprobs = self.sampler.sample_device(logits, rows, out=self.runner.token_out)

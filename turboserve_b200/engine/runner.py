@@ -100,11 +100,12 @@ class ModelRunner:
         self.num_steps = 0
         self.num_graph_replays = 0
         self.num_graph_captures = 0
-        self.graph_sampler = None
-        """A sampler with per-slot options (``Sampler.use_slots``): captured decode graphs then end with
-        its kernel, which leaves the step's token ids in :attr:`token_buffer` (:attr:`sampled_in_graph`)."""
-        self.sampled_in_graph = False
-        """Whether the step that ran last was a graph replay that sampled its own tokens."""
+        self.step_sampler = None
+        """A sampler with per-slot options (``Sampler.use_slots``): a step that is asked to sample, and
+        every captured decode graph, then ends with its kernel, which leaves the step's token ids (and
+        log-probabilities) in :attr:`token_buffer` (:attr:`sampled_in_step`)."""
+        self.sampled_in_step = False
+        """Whether the step that ran last sampled its own tokens."""
         self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, StaticBatch, torch.Tensor]] = {}
         self._graph_buckets: list[int] = []
         self._graph_widths: list[int] = []
@@ -123,12 +124,17 @@ class ModelRunner:
         self.num_steps += 1
         return self.model.forward(ctx, self.storage)
 
-    def step(self, slices: Sequence[RequestSlice], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
+    def step(self, slices: Sequence[RequestSlice], device_tokens: torch.Tensor | None = None,
+             sample: bool = False) -> torch.Tensor | None:
         """Pack ``slices`` and run them; logits ``[wanted rows, vocab]`` fp32, in slice order.
 
         ``device_tokens`` (int32, on the device) replaces the token ids of the slices, which must
         then bring one token each: slice ``i`` runs ``device_tokens[i]``. It lets a decode step be
         launched while the ids it runs on, sampled by the step before, are still on the device.
+
+        ``sample`` asks the step to end with :attr:`step_sampler` (if there is one, and no slice
+        wants more than one row): one token per wanted row, by the options of the row's state slot,
+        into :attr:`token_out`; :attr:`sampled_in_step` says whether it did.
         """
         vocab = self.model.vocab_size
         if device_tokens is not None:
@@ -140,15 +146,24 @@ class ModelRunner:
                     if not 0 <= int(token) < vocab:
                         raise ValueError(f"token id {token} is outside the vocabulary of {vocab}")
         if self._graph_buckets and self._is_plain_decode(slices):
-            return self._replay_decode(slices, device_tokens)
-        self.sampled_in_graph = False
+            return self._replay_decode(slices, device_tokens)  # samples whether asked or not: it is part of the graph
+        self.sampled_in_step = False
         batch = self.build_batch(slices)
         if device_tokens is not None:
             batch.token_ids[: len(slices)].copy_(device_tokens[: len(slices)])
-        if self.graph_sampler is not None:
-            # what a repetition penalty will need once these requests decode from a graph: their tokens, by slot
-            self.graph_sampler.mark_seen(batch.token_ids, batch.seq_of_token, batch.state_slots, batch.num_tokens)
-        return self.run(batch)
+        if self.step_sampler is not None:
+            # what a repetition penalty needs: the tokens of the requests that have one, by slot
+            self.step_sampler.mark_seen(batch.token_ids, batch.seq_of_token, batch.state_slots, batch.num_tokens)
+        logits = self.run(batch)
+        rows = batch.num_logit_rows
+        if (sample and self.step_sampler is not None and logits is not None and 0 < rows <= self.token_out.numel()
+                and all(len(piece.want) <= 1 for piece in slices)):
+            with torch.inference_mode():
+                self.step_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens, rows,
+                                                 self.token_out, row_token=batch.logit_rows, step_tokens=batch.token_ids,
+                                                 logprobs=self.logprob_out)
+            self.sampled_in_step = True
+        return logits
 
     # -- decode steps from captured graphs -------------------------------------------------------
 
@@ -226,11 +241,11 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = self.run(static.batch)
-            if self.graph_sampler is not None:
-                batch = static.batch
-                self.graph_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
-                                                  bucket, self.token_out, step_tokens=batch.token_ids,
-                                                  logprobs=self.logprob_out)
+            if self.step_sampler is not None:
+                batch = static.batch  # row i holds the logits of token i, which is request i's (or padding)
+                self.step_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
+                                                 bucket, self.token_out, step_tokens=batch.token_ids,
+                                                 logprobs=self.logprob_out)
         entry = (graph, static, logits)
         self._graphs[(bucket, skew)] = entry
         self.num_graph_captures += 1
@@ -281,7 +296,7 @@ class ModelRunner:
         graph.replay()
         self.num_steps += 1
         self.num_graph_replays += 1
-        self.sampled_in_graph = self.graph_sampler is not None
+        self.sampled_in_step = self.step_sampler is not None
         return logits[: len(slices)]
 
     def start_token_read(self, count: int) -> "TokenRead":

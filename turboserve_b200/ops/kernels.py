@@ -273,35 +273,45 @@ def sample(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor, *, nu
 
 def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor, num_rows: int, *, temperature: torch.Tensor,
                  top_k: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor, prompt_len: torch.Tensor,
-                 row_slot: torch.Tensor, row_seq: torch.Tensor | None, row_context: torch.Tensor, partial: torch.Tensor,
-                 chunks: int, penalty: torch.Tensor | None = None, seen: torch.Tensor | None = None,
-                 step_tokens: torch.Tensor | None = None, want_logprob: torch.Tensor | None = None,
+                 seq_slot: torch.Tensor, seq_context: torch.Tensor, partial: torch.Tensor, chunks: int,
+                 row_token: torch.Tensor | None = None, seq_of_token: torch.Tensor | None = None,
+                 step_tokens: torch.Tensor | None = None, penalty: torch.Tensor | None = None,
+                 seen: torch.Tensor | None = None, want_logprob: torch.Tensor | None = None,
                  logprobs: torch.Tensor | None = None) -> None:
-    """One token per row with the options looked up by state slot (arrays over the slots); the index of
-    the token being generated is ``row_context[row] - prompt_len[slot]``. A row with ``row_seq < 0`` is
-    skipped. ``partial`` is zeroed int32 scratch of ``rows * (2 * chunks + 1)`` words; a row that needs
-    one pass only (greedy, or a draw without top-k and top-p) is cut into ``chunks`` blocks.
+    """One token per row with the options looked up by state slot (arrays over the slots).
+
+    A row finds its request through a step's own index arrays: ``row_token`` (per row: the step's
+    token whose logits the row holds; without it the row itself), ``seq_of_token`` (per token: its
+    request in the step, negative for padding, whose row is skipped; without it the token itself),
+    ``seq_slot`` and ``seq_context`` (per request: its state slot and its length after the step).
+    The index of the token being generated is ``seq_context - prompt_len[slot]``. ``partial`` is
+    zeroed int32 scratch of ``rows * (2 * chunks + 1)`` words; a row that needs one pass only
+    (greedy, or a draw without top-k and top-p) is cut into ``chunks`` blocks.
 
     ``penalty`` (per slot) goes with ``seen`` (int32 ``[slots, ceil(vocab / 32)]``: the bitmap of the
-    tokens each slot's request holds) and ``step_tokens`` (per row: the token the request ran in this
-    step, which joins the bitmap first). ``want_logprob`` (per slot, int32) goes with ``logprobs``
-    (float32 per row): the log-probability of the chosen token under the penalised row."""
+    tokens each slot's request holds); ``step_tokens`` (per token of the step: its id) lets a row
+    add the token its logits come from to that bitmap first. ``want_logprob`` (per slot, int32)
+    goes with ``logprobs`` (float32 per row): the log-probability of the chosen token under the
+    penalised row."""
     _need(logits, torch.float32, "logits"); _need(work, torch.float32, "work"); _need(tokens, torch.int32, "tokens")
     vocab = logits.shape[1]
     if work.numel() < num_rows * vocab or not work.is_contiguous():
         raise KernelError("sample_slots: work must hold rows * vocab floats")
     for name, tensor, dtype in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
                                 ("top_p", top_p, torch.float32), ("seed", seed, torch.int64), ("prompt_len", prompt_len, torch.int32),
-                                ("row_slot", row_slot, torch.int32), ("row_context", row_context, torch.int32),
+                                ("seq_slot", seq_slot, torch.int32), ("seq_context", seq_context, torch.int32),
                                 ("partial", partial, torch.int32)):
         _need(tensor, dtype, name)
-    for name, tensor, dtype in (("row_seq", row_seq, torch.int32), ("penalty", penalty, torch.float32), ("seen", seen, torch.int32),
+    for name, tensor, dtype in (("row_token", row_token, torch.int32), ("seq_of_token", seq_of_token, torch.int32),
+                                ("penalty", penalty, torch.float32), ("seen", seen, torch.int32),
                                 ("step_tokens", step_tokens, torch.int32), ("want_logprob", want_logprob, torch.int32),
                                 ("logprobs", logprobs, torch.float32)):
         if tensor is not None:
             _need(tensor, dtype, name)
     if partial.numel() < num_rows * (2 * chunks + 1):
         raise KernelError("sample_slots: partial is too small")
+    if row_token is not None and row_token.numel() < num_rows:
+        raise KernelError("sample_slots: row_token has fewer entries than rows")
     seen_words = 0
     if penalty is not None:
         if seen is None or seen.dim() != 2 or not seen.is_contiguous() or seen.shape[1] * 32 < vocab or seen.shape[0] < penalty.numel():
@@ -309,12 +319,12 @@ def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
         seen_words = seen.shape[1]
     if (want_logprob is None) != (logprobs is None) or (logprobs is not None and logprobs.numel() < num_rows):
         raise KernelError("sample_slots: want_logprob and logprobs (one per row) go together")
-    fn = _fn("sampling", "ts_sample_slots", [c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 10 + [c_int] +
-             [c_void_p] * 3 + [c_int] + [c_void_p] * 3)
+    fn = _fn("sampling", "ts_sample_slots", [c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 12 + [c_int] +
+             [c_void_p] * 3 + [c_int] + [c_void_p] * 2)
     _check(fn(_ptr(logits), logits.stride(0), _ptr(work), num_rows, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
-              _ptr(seed), _ptr(prompt_len), _ptr(row_slot), _ptr(row_seq), _ptr(row_context), _ptr(tokens), _ptr(partial),
-              int(chunks), _ptr(penalty), _ptr(want_logprob), _ptr(seen if penalty is not None else None), seen_words,
-              _ptr(step_tokens), _ptr(logprobs), _stream()),
+              _ptr(seed), _ptr(prompt_len), _ptr(row_token), _ptr(seq_of_token), _ptr(seq_slot), _ptr(seq_context),
+              _ptr(step_tokens), _ptr(tokens), _ptr(partial), int(chunks), _ptr(penalty), _ptr(want_logprob),
+              _ptr(seen if penalty is not None else None), seen_words, _ptr(logprobs), _stream()),
            "sample_slots", launches=2)  # the one-pass kernel, then the cluster kernel for rows with filters
 
 

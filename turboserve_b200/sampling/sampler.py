@@ -12,13 +12,14 @@ takes the argmax kernel, which needs no scratch.
 Per-request options also live on the device, by state slot (:class:`SlotOptions`): they are
 written once, when a request is admitted, and a decode step finds them through the step's
 ``state_slots``; the index of the token being generated follows from the request's length, so
-nothing has to be sent or advanced per step and the sampler is part of a captured decode graph
-(:meth:`Sampler.sample_by_slot`). The history that a repetition penalty needs is there too, as
-one bit per vocabulary entry and slot: the tokens a step runs are marked by
-:meth:`Sampler.mark_seen` (portions of prompts, and everything that is computed again after a
-preemption) or by the sampling kernel itself (the one token a request ran in a decode step), so a
-penalised row needs nothing from the host either. Steps that are not replayed from a graph are
-sampled by :meth:`Sampler.sample_device`, with the options and histories sent along.
+nothing has to be sent or advanced per step, and a step ends with the sampling kernel, inside
+the captured graph where there is one (:meth:`Sampler.sample_by_slot`). The history that a
+repetition penalty needs is there too, as one bit per vocabulary entry and slot: the tokens a
+step runs are marked by :meth:`Sampler.mark_seen` (portions of prompts, and everything that is
+computed again after a preemption) or by the sampling kernel itself (the one token a request ran
+in a replayed decode step), so a penalised row needs nothing from the host either.
+:meth:`Sampler.sample_device` is the same sampler for callers that have no slots: options and
+histories come as lists and go up with the call.
 """
 
 from __future__ import annotations
@@ -132,24 +133,29 @@ class Sampler:
         self._scratch(num_slots, vocab)
         return self.slots
 
-    def sample_by_slot(self, logits: torch.Tensor, row_slot: torch.Tensor, row_seq: torch.Tensor | None,
-                       row_context: torch.Tensor, num_rows: int, out: torch.Tensor,
-                       step_tokens: torch.Tensor | None = None, logprobs: torch.Tensor | None = None) -> torch.Tensor:
+    def sample_by_slot(self, logits: torch.Tensor, seq_slot: torch.Tensor, seq_of_token: torch.Tensor | None,
+                       seq_context: torch.Tensor, num_rows: int, out: torch.Tensor, *,
+                       row_token: torch.Tensor | None = None, step_tokens: torch.Tensor | None = None,
+                       logprobs: torch.Tensor | None = None) -> torch.Tensor:
         """Sample ``num_rows`` rows whose options are in :attr:`slots`; ids into ``out``. Allocates nothing.
 
-        ``step_tokens`` (per row: the token the row's request ran in this step) joins the request's
-        history before a penalty reads it; without it the history is what :meth:`mark_seen` has
-        marked. ``logprobs`` (float32 per row) takes the log-probability of the chosen token for
-        the rows whose request asked for it; without it nobody gets one.
+        The arguments are a step's own index arrays: ``row_token`` (per row: the token whose logits
+        it holds; without it row ``i`` is token ``i``), ``seq_of_token`` (per token: its request in the
+        step, negative for padding), ``seq_slot`` and ``seq_context`` (per request: state slot, length
+        after the step). ``step_tokens`` (per token: its id) joins the request's history before a
+        penalty reads it; without it the history is what :meth:`mark_seen` has marked. ``logprobs``
+        (float32 per row) takes the log-probability of the chosen token for the rows whose request
+        asked for it; without it nobody gets one.
         """
         if self.slots is None or self._partial is None:
             raise RuntimeError("use_slots() first")
         slots = self.slots
         kernels.sample_slots(
             logits, self._scratch(num_rows, logits.shape[1]), out, num_rows, temperature=slots.temperature, top_k=slots.top_k,
-            top_p=slots.top_p, seed=slots.seed, prompt_len=slots.prompt_len, row_slot=row_slot, row_seq=row_seq,
-            row_context=row_context, partial=self._partial, chunks=SLOT_CHUNKS, penalty=slots.penalty, seen=slots.seen,
-            step_tokens=step_tokens, want_logprob=slots.want_logprob if logprobs is not None else None, logprobs=logprobs,
+            top_p=slots.top_p, seed=slots.seed, prompt_len=slots.prompt_len, seq_slot=seq_slot, seq_context=seq_context,
+            partial=self._partial, chunks=SLOT_CHUNKS, row_token=row_token, seq_of_token=seq_of_token, step_tokens=step_tokens,
+            penalty=slots.penalty, seen=slots.seen, want_logprob=slots.want_logprob if logprobs is not None else None,
+            logprobs=logprobs,
         )
         return out[:num_rows]
 
