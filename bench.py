@@ -152,8 +152,8 @@ def weight_bytes(model) -> int:
     """Bytes a decode step has to read of the weights: everything but the embedding table."""
     total = 0
     for p in model.named_params():
-        if p.name == model.spec.names.embedding and not model.spec.tie_word_embeddings:
-            continue
+        if model.parts_list[p.owner] is model.embedding and not model.spec.tie_word_embeddings:
+            continue  # a decode step reads a few rows of the table
         count = 1
         for s in p.spec.shape:
             count *= s

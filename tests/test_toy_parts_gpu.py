@@ -1,5 +1,6 @@
 """Toy parts defined here and nowhere else: a feed-forward with routing and another position
-encoding, in different layers of one model.
+encoding, in different layers of one model; a position encoding that is no rotation; an
+embedding and a head of their own around the layers.
 
 They are registered by kind, named in a ``LayerSpec``, built by the random-weights mode and the
 loader from their ``param_specs``, and stepped through replay whole, cut and mixed, without a
@@ -273,3 +274,130 @@ def test_toy_position_encoding_that_is_not_a_rotation(tmp_path):
     finally:
         unregister_architecture("ToyWavesForCausalLM")
         POSITIONS.unregister("toy_waves")
+
+
+PLACE_PERIOD = 7
+EMBED_SCALE = 1.5
+HEAD_SCALE = 0.5
+
+
+def test_toy_embedding_and_head_around_the_layers(tmp_path):
+    """An embedding that scales the token's row and adds a row chosen by the position, and a head
+    tied to the embedding's table that scales its logits and adds a bias of its own: both are
+    registered here, declare their tensors (``model.embed_tokens.place.weight``, ``lm_head.bias``),
+    and the model, the loader, the random-weights mode and replay use them as they are."""
+    from dataclasses import dataclass
+
+    from safetensors.torch import load_file
+
+    from turboserve_b200.config import LayerSpec, ModelSpec, PartSpec, register_architecture, unregister_architecture
+    from turboserve_b200.models import DecoderModel
+    from turboserve_b200.ops import kernels
+    from turboserve_b200.parts import EMBEDDINGS, HEADS, LogitHead, ParamSpec, TokenEmbedding, register_embedding, register_head
+    from turboserve_b200.replay import Replayer
+    from turboserve_b200.weights import load_weights, write_random_model
+
+    class PlacedEmbedding(TokenEmbedding):
+        def __init__(self, spec, hidden_size, vocab_size, dtype, device):
+            self.hidden, self.vocab, self.period, self.scale = hidden_size, vocab_size, int(spec["period"]), float(spec["scale"])
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.vocab, self.hidden)), ParamSpec("place.weight", (self.period, self.hidden))]
+
+        def bind(self, tensors):
+            self.table, self.place = tensors["weight"].contiguous(), tensors["place.weight"]
+
+        def forward(self, residual, ctx):
+            n = ctx.batch.num_tokens
+            kernels.embedding(ctx.batch.token_ids, self.table, residual, ctx.status)
+            residual[:n].mul_(self.scale).add_(self.place.float()[ctx.batch.positions[:n].long() % self.period])
+
+    class BiasedHead(LogitHead):
+        def __init__(self, spec, hidden_size, vocab_size, dtype, device, tied=False):
+            self.hidden, self.vocab, self.tied, self.scale = hidden_size, vocab_size, tied, float(spec["scale"])
+            self.weight = None
+
+        def param_specs(self):
+            own = [] if self.tied else [ParamSpec("weight", (self.vocab, self.hidden))]
+            return own + [ParamSpec("bias", (self.vocab,), role="bias", init="bias_normal")]
+
+        def bind(self, tensors):
+            self.bias = tensors["bias"]
+            if not self.tied:
+                self.weight = tensors["weight"]
+
+        def tie(self, table):
+            self.weight = table
+
+        def forward(self, rows_in, logits, num_rows, ctx):
+            logits[:num_rows] = (rows_in[:num_rows].float() @ self.weight.float().T) * self.scale + self.bias
+
+    register_embedding("toy_placed", PlacedEmbedding)
+    register_head("toy_biased", BiasedHead)
+
+    @dataclass(frozen=True)
+    class AroundConfig:
+        hidden_size: int
+        vocab_size: int
+        tie_word_embeddings: bool
+        architecture: str = "ToyAroundForCausalLM"
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["hidden_size"], data["vocab_size"], data["tie_word_embeddings"])
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], hidden_size=self.hidden_size, vocab_size=self.vocab_size,
+                        tie_word_embeddings=self.tie_word_embeddings)
+
+        def to_model_spec(self):
+            norm = PartSpec("rms_norm", {"eps": 1e-5})
+            attn = PartSpec("attention", dict(num_heads=3, num_kv_heads=1, head_dim=16, qkv_bias=False, window=None))
+            dense = PartSpec("gated_mlp", {"intermediate_size": 48})
+            layers = (LayerSpec(attn, dense, norm, norm, PartSpec("rotary", dict(rotary_dim=16, theta=1e4))),)
+            return ModelSpec(self.architecture, self.hidden_size, self.vocab_size, layers, ModelSpec.sequential(1), norm,
+                             embedding=PartSpec("toy_placed", {"period": PLACE_PERIOD, "scale": EMBED_SCALE}),
+                             head=PartSpec("toy_biased", {"scale": HEAD_SCALE}), tie_word_embeddings=self.tie_word_embeddings)
+
+    register_architecture("ToyAroundForCausalLM", AroundConfig,
+                          lambda config, dtype, device: DecoderModel(config.to_model_spec(), dtype, device))
+
+    def plain(weights, ids, tied):
+        w = {k: v.double() for k, v in weights.items()}
+        pos = torch.arange(len(ids))
+        h = w["model.embed_tokens.weight"][torch.tensor(ids)] * EMBED_SCALE + w["model.embed_tokens.place.weight"][pos % PLACE_PERIOD]
+        rotary = 1.0 / (1e4 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+        p = "model.layers.0."
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], 1e-5)
+        h = h + plain_attention(x, w, p + "self_attn.", pos, rotary)
+        x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-5)
+        h = h + P.mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], "silu")
+        matrix = w["model.embed_tokens.weight"] if tied else w["lm_head.weight"]
+        return (P.rms_norm(h, w["model.norm.weight"], 1e-5) @ matrix.T) * HEAD_SCALE + w["lm_head.bias"]
+
+    try:
+        for tied in (True, False):
+            config = AroundConfig(hidden_size=40, vocab_size=70, tie_word_embeddings=tied)
+            folder = write_random_model(config, 21, tmp_path / f"around{int(tied)}", torch.float32)
+            weights = load_file(str(folder / "model.safetensors"))
+            assert weights["model.embed_tokens.place.weight"].shape == (PLACE_PERIOD, 40) and weights["lm_head.bias"].shape == (70,)
+            assert ("lm_head.weight" in weights) == (not tied)
+            assert weights["lm_head.bias"].abs().max() > 0
+            requests = traces.make_requests(70, [33, 8, 47, 21], seed=24)
+            ref = {rid: plain(weights, ids, tied) for rid, ids in requests.items()}
+            for builder, kwargs in ((traces.whole, {}), (traces.changing_portions, {"sizes": (5, 2, 11, 1)}), (traces.mixed, {"seed": 3, "max_live": 3})):
+                steps, max_tokens = builder(requests, **kwargs)
+                replayer = Replayer(folder, "float32", max_tokens)
+                assert (replayer.model.head.weight is replayer.model.embedding.table) == tied
+                assert not replayer.model.graph_safe  # the toy parts did not say they were
+                got = traces.collect(requests, steps, traces.replay(replayer, steps))
+                for rid in requests:
+                    assert torch.allclose(got[rid].double(), ref[rid], atol=3e-5), (tied, builder.__name__, rid, (got[rid].double() - ref[rid]).abs().max())
+        # a tied checkpoint may still hold the head's copy of the table (not loaded), but never lacks the head's own bias
+        model = DecoderModel(AroundConfig(40, 70, True).to_model_spec(), torch.float32, "cuda")
+        assert model.optional_names() == {"lm_head.weight"}
+        assert [p.name for p in model.named_params()][-1] == "lm_head.bias"
+    finally:
+        unregister_architecture("ToyAroundForCausalLM")
+        EMBEDDINGS.unregister("toy_placed")
+        HEADS.unregister("toy_biased")

@@ -40,7 +40,7 @@ def test_load_keeps_dtypes_by_role(tmp_path):
     folder = write_random_model(config, 1, tmp_path / "m", torch.float32)
     stored = load_weights(model, folder)
     assert set(stored.values()) == {"F32"}
-    assert model.embedding.dtype == torch.bfloat16 and model.head.dtype == torch.bfloat16
+    assert model.embedding.table.dtype == torch.bfloat16 and model.head.weight.dtype == torch.bfloat16
     assert model.blocks[0].mixer.qkv.dtype == torch.bfloat16
     assert model.blocks[0].mixer.qkv_b.dtype == torch.float32  # a bias stored in 32-bit stays so
     assert model.final_norm.gain.dtype == torch.float32
@@ -48,7 +48,7 @@ def test_load_keeps_dtypes_by_role(tmp_path):
     assert torch.equal(model.final_norm.gain, raw["model.norm.weight"])
     q = raw["model.layers.1.self_attn.q_proj.weight"].to(torch.bfloat16)
     assert torch.equal(model.blocks[1].mixer.qkv[: q.shape[0]], q)
-    assert model.head is not model.embedding
+    assert model.head.weight is not model.embedding.table
 
 
 def test_tied_head_shares_storage_and_tolerates_a_copy(tmp_path):
@@ -59,7 +59,7 @@ def test_tied_head_shares_storage_and_tolerates_a_copy(tmp_path):
     tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
     save_file(tensors, str(folder / "model.safetensors"))
     load_weights(model, folder)
-    assert model.head is model.embedding
+    assert model.head.weight is model.embedding.table
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
@@ -142,7 +142,7 @@ def test_exporter_prefixes_are_rewritten_before_names_are_compared(tmp_path):
         save_file(renamed, str(folder / "model.safetensors"))
         _, fresh = build(TINY_B)
         load_weights(fresh, folder)
-        assert torch.equal(fresh.head, plain["lm_head.weight"]) and torch.equal(fresh.embedding, plain["model.embed_tokens.weight"])
+        assert torch.equal(fresh.head.weight, plain["lm_head.weight"]) and torch.equal(fresh.embedding.table, plain["model.embed_tokens.weight"])
         assert torch.equal(fresh.blocks[2].feed_forward.down, plain["model.layers.2.mlp.down_proj.weight"])
     renamed["transformer.extra.weight"] = torch.zeros(2)
     save_file(renamed, str(folder / "model.safetensors"))

@@ -78,14 +78,15 @@ class TensorNames:
     """How an architecture's checkpoint names its tensors.
 
     ``layer`` is formatted with the layer index; the four part prefixes are appended to it and
-    each part appends its own local names (``q_proj.weight`` and so on). ``prefix_rewrites``
+    each part appends its own local names (``q_proj.weight`` and so on). ``embedding``, ``head``
+    and ``final_norm`` are the prefixes of the parts around the layers. ``prefix_rewrites``
     are prefixes some exporters put in front of the decoder stack, with what the names above
     expect in their place; the first that matches a checkpoint name is applied, once
     (``src/turboserve/engine/model/weights.py:56-61,181-196``).
     """
 
-    embedding: str = "model.embed_tokens.weight"
-    head: str = "lm_head.weight"
+    embedding: str = "model.embed_tokens."
+    head: str = "lm_head."
     final_norm: str = "model.norm."
     layer: str = "model.layers.{index}."
     mixer: str = "self_attn."
@@ -110,6 +111,8 @@ class ModelSpec:
     layers: tuple[LayerSpec, ...]
     order: tuple[LayerRun, ...]
     final_norm: PartSpec
+    embedding: PartSpec = PartSpec("table")
+    head: PartSpec = PartSpec("linear")
     tie_word_embeddings: bool = False
     names: TensorNames = field(default_factory=TensorNames)
     eos_token_ids: tuple[int, ...] = ()

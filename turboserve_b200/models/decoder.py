@@ -1,7 +1,8 @@
 """The decoder every architecture is built as: embedding, a run order of layers, norm, head.
 
 The model is assembled from a :class:`~turboserve_b200.config.ModelSpec` through the part
-registries and knows nothing about any particular architecture. It replaces the reference's
+registries (the embedding and the head are parts too) and knows nothing about any particular
+architecture. It replaces the reference's
 ``Decoder`` / ``CausalLM`` pair (``src/turboserve/engine/model/model.py:51-108,111-315``):
 ``forward`` runs the step's packed tokens through the layers against the cache and returns
 fp32 logits only at the rows that were asked for (``compute_logits``, ``:220-244``).
@@ -15,9 +16,7 @@ import torch
 
 from ..cache.storage import CachePlan, CacheStorage, plan_cache
 from ..config.model_spec import ModelSpec
-from ..ops import kernels
-from ..ops.linear import linear
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, UNDECLARED_SCRATCH_WIDTHS, ParamSpec, Part
+from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, UNDECLARED_SCRATCH_WIDTHS, ParamSpec, Part
 
 
 @dataclass(frozen=True)
@@ -26,7 +25,7 @@ class NamedParam:
 
     name: str
     spec: ParamSpec
-    owner: int  # index into DecoderModel.parts_list, -1 for embedding / head
+    owner: int  # index into DecoderModel.parts_list
     local: str
 
 
@@ -36,8 +35,9 @@ class DecoderModel:
         self.dtype = dtype
         self.device = torch.device(device)
         self.hidden_size, self.vocab_size = spec.hidden_size, spec.vocab_size
-        self.parts_list: list[Part] = []
-        self._part_prefix: list[str] = []
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, spec.hidden_size, spec.vocab_size, dtype, self.device)
+        self.parts_list: list[Part] = [self.embedding]
+        self._part_prefix: list[str] = [spec.names.embedding]
         self.blocks = []
         reads_only = [True] * len(spec.layers)
         for run in spec.order:
@@ -58,29 +58,33 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.hidden_size, dtype, self.device)
         self.parts_list.append(self.final_norm)
         self._part_prefix.append(spec.names.final_norm)
-        self.embedding: torch.Tensor | None = None
-        self.head: torch.Tensor | None = None
+        self.head = HEADS.get(spec.head.kind)(spec.head, spec.hidden_size, spec.vocab_size, dtype, self.device,
+                                              tied=spec.tie_word_embeddings)
+        self.parts_list.append(self.head)
+        self._part_prefix.append(spec.names.head)
         self.loaded = False
 
     # -- tensors ----------------------------------------------------------------------------
 
     def named_params(self) -> list[NamedParam]:
-        """Every tensor the checkpoint must hold, in a fixed order (the random-weights order)."""
-        spec = self.spec
-        out = [NamedParam(spec.names.embedding, ParamSpec("embedding", (spec.vocab_size, spec.hidden_size)), -1, "embedding")]
+        """Every tensor the checkpoint must hold, in a fixed order (the random-weights order):
+        the embedding's, the layers' in order, the final norm's, the head's."""
+        out = []
         for index, (part, prefix) in enumerate(zip(self.parts_list, self._part_prefix)):
             for p in part.param_specs():
                 out.append(NamedParam(prefix + p.name, p, index, p.name))
-        if not spec.tie_word_embeddings:
-            out.append(NamedParam(spec.names.head, ParamSpec("head", (spec.vocab_size, spec.hidden_size)), -1, "head"))
         names = [p.name for p in out]
         if len(set(names)) != len(names):
             raise ValueError("two parts declare a tensor of the same name")
         return out
 
     def optional_names(self) -> set[str]:
-        """Names a checkpoint may hold that are not loaded (the tied head's copy)."""
-        return {self.spec.names.head} if self.spec.tie_word_embeddings else set()
+        """Names a checkpoint may hold that are not loaded (the tied head's copy of the embedding)."""
+        if not self.spec.tie_word_embeddings:
+            return set()
+        untied = HEADS.get(self.spec.head.kind)(self.spec.head, self.hidden_size, self.vocab_size, self.dtype, self.device, tied=False)
+        own = {p.name for p in self.head.param_specs()}
+        return {self.spec.names.head + p.name for p in untied.param_specs() if p.name not in own}
 
     def bind_stream(self, fetch) -> None:
         """Hand every part its tensors, one part at a time.
@@ -104,18 +108,15 @@ class DecoderModel:
             if p.owner != owner:
                 flush()
                 current, owner = {}, p.owner
-            if p.owner >= 0:
-                current[p.local] = t
-            elif p.local == "embedding":
-                self.embedding = t.contiguous()
-            else:
-                self.head = t.contiguous()
+            current[p.local] = t
         flush()
-        if self.spec.tie_word_embeddings:
-            self.head = self.embedding
-        for index, part in enumerate(self.parts_list):
+        for part in self.parts_list:
             if not part.param_specs():
                 part.bind({})
+        if self.spec.tie_word_embeddings:
+            if self.embedding.table is None:
+                raise ValueError(f"the head is tied, but the embedding of kind {self.spec.embedding.kind!r} has no table to share")
+            self.head.tie(self.embedding.table)
         self.loaded = True
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -141,15 +142,17 @@ class DecoderModel:
     # -- what the parts declare -----------------------------------------------------------------
 
     def scratch_bytes_per_token(self, itemsize: int) -> int:
-        """Scratch a step holds per token: the fp32 residual, the normed rows, and the most that
-        any layer's mixer and feed-forward declare (buffers are shared between layers by name)."""
+        """Scratch a step holds per token: the fp32 residual, the normed rows, the most that any
+        layer's mixer and feed-forward declare (buffers are shared between layers by name), and
+        what the embedding and the head declare."""
         def declared(part: Part) -> int:
             own = part.scratch_per_token()
             return UNDECLARED_SCRATCH_WIDTHS * self.hidden_size if own is None else int(own)
 
         mixers = max(declared(block.mixer) for block in self.blocks)
         feed_forwards = max(declared(block.feed_forward) for block in self.blocks)
-        return 4 * self.hidden_size + itemsize * (self.hidden_size + mixers + feed_forwards)
+        around = declared(self.embedding) + declared(self.head)
+        return 4 * self.hidden_size + itemsize * (self.hidden_size + mixers + feed_forwards + around)
 
     @property
     def graph_safe(self) -> bool:
@@ -171,7 +174,7 @@ class DecoderModel:
         batch = ctx.batch
         n = batch.num_tokens
         residual = ctx.buffer("model.residual", (n, self.hidden_size), torch.float32)
-        kernels.embedding(batch.token_ids, self.embedding, residual, ctx.status)
+        self.embedding.forward(residual, ctx)
         pending = None
         for run_index, run in enumerate(self.spec.order):
             ctx.run_index = run_index
@@ -182,5 +185,5 @@ class DecoderModel:
         final = ctx.buffer("model.final", (rows, self.hidden_size))
         self.final_norm.forward_rows(residual, pending, batch.logit_rows, rows, final, ctx)
         logits = ctx.buffer("model.logits", (rows, self.vocab_size), torch.float32)
-        linear(final, self.head, logits, None, rows, ctx)
+        self.head.forward(final, logits, rows, ctx)
         return logits

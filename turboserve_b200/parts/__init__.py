@@ -1,14 +1,14 @@
-"""Parts a layer is put together from; importing the package registers the built-in kinds."""
+"""Parts a model is put together from; importing the package registers the built-in kinds."""
 
 from .base import (
-    BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer, Norm, PagedKVNeed, ParamSpec, Part,
-    PositionEncoding, StateNeed, register_block, register_feed_forward, register_mixer, register_norm,
-    register_position,
+    BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, FeedForward, LogitHead, Mixer, Norm, PagedKVNeed,
+    ParamSpec, Part, PositionEncoding, StateNeed, TokenEmbedding, register_block, register_embedding, register_feed_forward,
+    register_head, register_mixer, register_norm, register_position,
 )
-from . import attention, block, mlp, norm, rope  # noqa: F401,E402  (registration)
+from . import attention, block, mlp, norm, rope, vocabulary  # noqa: F401,E402  (registration)
 
 __all__ = [
-    "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "Mixer", "Norm", "PagedKVNeed",
-    "ParamSpec", "Part", "PositionEncoding", "StateNeed", "register_block", "register_feed_forward",
-    "register_mixer", "register_norm", "register_position",
+    "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "LogitHead", "Mixer",
+    "Norm", "PagedKVNeed", "ParamSpec", "Part", "PositionEncoding", "StateNeed", "TokenEmbedding", "register_block",
+    "register_embedding", "register_feed_forward", "register_head", "register_mixer", "register_norm", "register_position",
 ]

@@ -1,7 +1,8 @@
 """Interfaces of the parts a layer is put together from, and their registries.
 
 A layer is a *mixer* (attention here), a *feed-forward*, two *norms* and optionally a
-*position encoding*, arranged by a *block*. Every part
+*position encoding*, arranged by a *block*; around the layers stand a *token embedding* (ids to
+the residual stream) and a *logit head* (final rows to logits). Every part
 
 * is chosen by ``PartSpec.kind`` through a registry, layer by layer, so one model can have
   different mixers and feed-forwards in different layers;
@@ -23,6 +24,8 @@ Constructor signatures
     norm           ``cls(spec, hidden_size, dtype, device)``
     position       ``cls(spec, device)``
     block          ``cls(mixer, feed_forward, mixer_norm, feed_forward_norm)``
+    embedding      ``cls(spec, hidden_size, vocab_size, dtype, device)``
+    head           ``cls(spec, hidden_size, vocab_size, dtype, device, tied=False)``
 """
 
 from __future__ import annotations
@@ -149,6 +152,36 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class TokenEmbedding(Part):
+    """Turns the step's token ids into the residual stream.
+
+    ``forward(residual, ctx)`` fills the float32 ``residual`` ``[tokens, hidden]`` for the packed
+    tokens of ``ctx.batch`` (``token_ids``, and ``positions`` or anything else of the batch it
+    needs). ``table`` is the ``[vocab, hidden]`` matrix that a tied head multiplies by, if the
+    embedding has one to share.
+    """
+
+    table: torch.Tensor | None = None
+
+    def forward(self, residual: torch.Tensor, ctx: Any) -> None:
+        raise NotImplementedError
+
+
+class LogitHead(Part):
+    """Turns the final normed rows into float32 logits.
+
+    ``forward(rows_in, logits, num_rows, ctx)`` writes ``logits[:num_rows]`` (float32
+    ``[rows, vocab]``) from ``rows_in`` (``[rows, hidden]``, activation dtype). A head built with
+    ``tied=True`` declares no matrix of its own and receives the embedding's through :meth:`tie`.
+    """
+
+    def tie(self, table: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def forward(self, rows_in: torch.Tensor, logits: torch.Tensor, num_rows: int, ctx: Any) -> None:
+        raise NotImplementedError
+
+
 class PositionEncoding:
     """Whatever turns positions into a change of queries and keys; a mixer calls :meth:`apply`.
 
@@ -244,6 +277,8 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("token embedding")
+HEADS = Registry("logit head")
 
 
 def register_mixer(kind: str, factory: Callable[..., Any]) -> None:
@@ -256,6 +291,14 @@ def register_feed_forward(kind: str, factory: Callable[..., Any]) -> None:
 
 def register_norm(kind: str, factory: Callable[..., Any]) -> None:
     NORMS.register(kind, factory)
+
+
+def register_embedding(kind: str, factory: Callable[..., Any]) -> None:
+    EMBEDDINGS.register(kind, factory)
+
+
+def register_head(kind: str, factory: Callable[..., Any]) -> None:
+    HEADS.register(kind, factory)
 
 
 def register_position(kind: str, factory: Callable[..., Any]) -> None:
