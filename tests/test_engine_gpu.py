@@ -218,6 +218,59 @@ def test_penalised_requests_through_preemption_and_reused_slots(model_folders):
     assert [o.output_tokens for o in outputs] == [30] * 6 and counts["checked"] == 180 and counts["logprobs"] == 60
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_random_arrivals_aborts_and_options_keep_every_sampled_id_right(model_folders, dtype):
+    """Forty requests with drawn lengths and options (greedy, temperature, filters, penalties,
+    log-probabilities) arrive at drawn steps in a pool that forces preemptions; some are aborted
+    while they run, also while a step launched ahead still holds them. Every id that is handed
+    out is what the plain sampler draws from the row of logits its step produced, every request
+    that was not aborted gets all its tokens, and nothing is left behind in the pool."""
+    import random
+
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    config, _ = P.read_model_folder(model_folders["D"])
+    rng = random.Random(31)
+    engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype=dtype, seed=9, scheduler=SchedulerConfig(
+        max_num_seqs=4, max_num_batched_tokens=48, block_size=8, num_blocks=18)))
+    counts = check_sampling_against_the_plain_sampler(engine)
+    arrivals = []
+    for i in range(40):
+        options = dict(max_tokens=rng.randint(1, 24), ignore_eos=True, temperature=rng.choice([0.0, 0.0, 0.7, 1.1]), seed=i)
+        if rng.random() < 0.4:
+            options.update(top_k=rng.choice([0, 5, 40]), top_p=rng.choice([1.0, 0.9, 0.6]))
+        if rng.random() < 0.5:
+            options["repetition_penalty"] = rng.choice([1.1, 1.5, 0.9])
+        options["logprobs"] = rng.random() < 0.3
+        arrivals.append((rng.randint(0, 60), f"r{i}", prompts_for(config, [rng.randint(1, 70)], seed=100 + i)[0], SamplingParams(**options)))
+    abort_steps = {rng.randint(5, 70) for _ in range(8)}
+    produced, finished, aborted = {}, {}, set()
+    with engine:
+        step = 0
+        while step < 80 or engine.has_unfinished():
+            for when, rid, prompt, sampling in arrivals:
+                if when == step:
+                    engine.add_request(rid, prompt, sampling)
+            if step in abort_steps and engine.scheduler._running:
+                victim = rng.choice(engine.scheduler._running).request_id  # it may be part of the step that is under way
+                assert engine.abort(victim)
+                aborted.add(victim)
+            for out in engine.step():
+                produced.setdefault(out.request_id, []).extend(out.new_token_ids)
+                if out.finished:
+                    finished[out.request_id] = out.finish_reason
+            step += 1
+            assert step < 2000
+        stats = engine.stats()
+        engine.scheduler.check_invariants()
+        assert engine.cache.free_pages() == [g.num_pages for g in engine.cache.groups]
+    assert len(aborted) >= 4 and stats["num_preemptions"] > 0 and stats["num_overlapped_steps"] > 5
+    for _, rid, _, sampling in arrivals:
+        if rid not in aborted:
+            assert len(produced[rid]) == sampling.max_tokens and finished[rid] == "length", rid
+    assert counts["checked"] >= sum(len(v) for v in produced.values()) and counts["logprobs"] > 20
+
+
 def test_long_decoding_through_many_pages_and_a_window(model_folders):
     from turboserve_b200 import SamplingParams
 
