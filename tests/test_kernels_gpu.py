@@ -1036,13 +1036,15 @@ def test_decode_attention_over_a_work_list(nh, nkv, page, window):
     assert (got - ref).abs().max().item() < 2e-2, (got - ref).abs().max().item()
 
 
-def test_the_two_tilings_of_the_float32_product_give_the_same_bits():
+def test_the_forms_of_the_float32_product_give_the_same_bits():
     """Rows 0..63 of a product of 200 rows (the 128x128 tiling) equal the product of those 64 rows alone
-    (the 64x64 tiling) bit for bit, at sizes that are no multiple of any tile and with unaligned rows."""
+    (the 64x64 tiling) bit for bit, and so do 1 to 16 of them through the weight-streaming form, at
+    sizes that are no multiple of any tile (k = 77 leaves a chunk of one float, n = 130 two features
+    in the last warp) and with unaligned rows."""
     from turboserve_b200.ops import kernels
 
     torch.manual_seed(9)
-    for k, n, pad in [(200, 150, 0), (1030, 257, 0), (77, 130, 3), (3584, 520, 0)]:
+    for k, n, pad in [(200, 150, 0), (1030, 257, 0), (77, 130, 3), (77, 130, 0), (3584, 520, 0), (18944, 64, 0)]:
         a = torch.randn(200, k + pad, device=DEV)[:, :k]   # pad: a row stride that is no multiple of four
         w = torch.randn(n, k + pad, device=DEV)[:, :k] / math.sqrt(k)
         bias = torch.randn(n, device=DEV)
@@ -1053,3 +1055,11 @@ def test_the_two_tilings_of_the_float32_product_give_the_same_bits():
         assert torch.equal(big[:64], small), (k, n, pad)
         ref = a.double() @ w.double().T + bias.double()
         assert (big.double() - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+        # and the weight-streaming form that up to 16 rows take when their stride is a multiple of four floats (else the 64x64 tiling again)
+        for rows in (1, 3, 8, 9, 16):
+            few = torch.full((rows, n), float("nan"), device=DEV)
+            kernels.gemm_simt(a[5:5 + rows], w, few, bias, rows)
+            assert torch.equal(few, big[5:5 + rows]), (k, n, pad, rows)
+            plain = torch.full((rows, n), float("nan"), device=DEV)
+            kernels.gemm_simt(a[5:5 + rows], w, plain, None, rows)
+            assert torch.isfinite(plain).all() and (plain.double() - (ref[5:5 + rows] - bias.double())).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
