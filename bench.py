@@ -128,7 +128,8 @@ class ClockSampler:
         }
 
 
-def build_runner(layers: int, max_seqs: int, context: int, seed: int = 0, shape: str = "7b", pages: int | None = None):
+def build_runner(layers: int, max_seqs: int, context: int, seed: int = 0, shape: str = "7b", pages: int | None = None,
+                 dtype=None):
     import torch
 
     from turboserve_b200.config import config_from_dict, lookup
@@ -136,7 +137,7 @@ def build_runner(layers: int, max_seqs: int, context: int, seed: int = 0, shape:
 
     raw = dict(SHAPES[shape][1], num_hidden_layers=layers)
     config = config_from_dict(raw)
-    model = lookup(config.architecture).build_model(config, torch.bfloat16, "cuda")
+    model = lookup(config.architecture).build_model(config, dtype or torch.bfloat16, "cuda")
     model.config = config
     model.init_random(seed)
     if pages is None:
@@ -419,33 +420,69 @@ def reference_arm(args, shape_name: str, shape_raw: dict) -> int:
     return 0
 
 
-def fp32_products() -> int:
-    """The true 32-bit path's matrix product (FFMA, no tensor cores) at the 7B layer's shapes: one JSON line."""
+def fp32_products(layers: int = 28, steps: int = 8) -> int:
+    """The true 32-bit path (FFMA, no tensor cores): its matrix product at the 7B layer's shapes, every
+    weight from HBM (copies of a weight taken in turn, 600 MB of them), and one decode step of the
+    whole model in float32 at batch 8, context 4,096. One JSON line."""
     import torch
 
+    from turboserve_b200.engine.batch import RequestSlice, StaticBatch
     from turboserve_b200.ops.linear import linear
 
     shapes = {"qkv": (3584, 4608), "o": (3584, 3584), "gate_up": (3584, 37888), "down": (18944, 3584)}
     line = {"what": "float32 FFMA product (gemm_simt.cu), Qwen2-7B layer shapes", "unit": "TFLOP/s (rows 2048) and GB/s of weights (rows 8)"}
     for name, (k, n) in shapes.items():
-        w = torch.randn(n, k, device="cuda")
+        copies = max(2, -(-600_000_000 // (4 * k * n)))
+        ws = [torch.randn(n, k, device="cuda") for _ in range(copies)]
         for rows in (2048, 8):
             x = torch.randn(rows, k, device="cuda")
             out = torch.empty(rows, n, device="cuda")
-            for _ in range(2):
+            for w in ws[:2]:
                 linear(x, w, out)
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
-            for _ in range(3):
+            for w in ws:
                 linear(x, w, out)
             end.record()
             torch.cuda.synchronize()
-            seconds = begin.elapsed_time(end) / 3e3
+            seconds = begin.elapsed_time(end) / 1e3 / copies
             line[f"{name}_rows{rows}_ms"] = round(seconds * 1e3, 3)
             line[f"{name}_rows{rows}"] = round(2 * rows * k * n / seconds / 1e12, 2) if rows > 8 else round(4 * k * n / seconds / 1e9, 1)
-        del w
+        del ws
+    # one decode step of the whole model in float32 (no graphs on this path: every kernel is launched by the host)
+    batch, context = 8, CONTEXT
+    config, model, runner = build_runner(layers, batch, context, dtype=torch.float32)
+    width = context // PAGE
+    static = StaticBatch(batch, batch, [width], runner.device)
+    slices = [RequestSlice([7 + i], context - steps - 4, [list(range(i * width, (i + 1) * width))], i, [0]) for i in range(batch)]
+    static.load_decode(slices)
+    times = []
+    for step in range(steps + 2):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        runner.run(static.batch)
+        end.record()
+        torch.cuda.synchronize()
+        static.batch.positions.add_(1)
+        static.batch.context_lens.add_(1)
+        if step >= 2:
+            times.append(begin.elapsed_time(end))
+    runner.check_status()
+    ms = statistics.median(times)
+    weights = sum(4 * _count(p.spec.shape) for p in model.named_params() if model.parts_list[p.owner] is not model.embedding)
+    cache = batch * (context - 4) * layers * 2 * config.num_key_value_heads * config.head_dim * 4
+    line["decode_step"] = {"layers": layers, "layers_of_model": SHAPES["7b"][1]["num_hidden_layers"], "batch": batch, "context": context,
+                           "ms": round(ms, 2), "gb_per_s": round((weights + cache) / ms / 1e6, 1),
+                           "frac_of_hbm": round((weights + cache) / ms / 1e6 / load_peaks()["hbm_gbs"], 3)}
     print(json.dumps(line))
     return 0
+
+
+def _count(shape) -> int:
+    total = 1
+    for s in shape:
+        total *= s
+    return total
 
 
 def decode_attention_sweep() -> int:
