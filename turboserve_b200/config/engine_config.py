@@ -131,7 +131,7 @@ class EngineConfig(BaseModel):
     seed: int | None = None
     scheduler: SchedulerConfig = Field(default_factory=SchedulerConfig)
     cuda_graphs: bool = True
-    """Replay decode-only steps from captured CUDA graphs (bfloat16 path)."""
+    """Replay decode-only steps from captured CUDA graphs."""
 
     capture_graphs_at_start: bool = True
     """Capture the decode graphs of every batch size when the engine is built, instead of when a

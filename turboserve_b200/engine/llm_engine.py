@@ -101,7 +101,7 @@ class LLMEngine:
                 self.runner.step_sampler = self.sampler
             else:
                 self.runner.step_sampler = None  # graphs captured with another sampler: their ids are not used
-        if config.cuda_graphs and self.runner.dtype == torch.bfloat16 and hasattr(self.runner, "enable_graphs"):
+        if config.cuda_graphs and hasattr(self.runner, "enable_graphs"):
             pages = min(g.num_pages for g in self.runner.groups)
             longest = min(config.max_model_len or pages * config.block_size, pages * config.block_size)
             self.runner.enable_graphs(config.scheduler.max_num_seqs, longest, config.scheduler.max_num_batched_tokens)
