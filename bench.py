@@ -309,13 +309,13 @@ def prefill_flops(config, tokens: int) -> float:
     return config.num_hidden_layers * (per_layer + attention) + 2 * h * config.vocab_size
 
 
-def one_step(kind: str, layers: int, batch: int, shape: str = "7b") -> int:
+def one_step(kind: str, layers: int, batch: int, shape: str = "7b", float32: bool = False) -> int:
     """Three eager steps (no graph) of one kind, so that a profiler sees every kernel once per step."""
     import torch
 
     from turboserve_b200.engine.batch import RequestSlice, StaticBatch
 
-    config, model, runner = build_runner(layers, max(batch, 1), CONTEXT, shape=shape)
+    config, model, runner = build_runner(layers, max(batch, 1), CONTEXT, shape=shape, dtype=torch.float32 if float32 else None)
     width = CONTEXT // PAGE
     if kind == "decode":
         static = StaticBatch(batch, batch, [width], runner.device)
@@ -603,6 +603,7 @@ def main() -> int:
     parser.add_argument("--decode-attention-sweep", action="store_true", help="time the decode attention kernel alone at a few sizes and exit")
     parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
+    parser.add_argument("--float32", action="store_true", help="with --one-step: the true 32-bit path")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                         help="run three eager steps of that kind and exit (a small case for a profiler)")
     args = parser.parse_args()
@@ -629,7 +630,7 @@ def main() -> int:
     if args.sampling_sweep:
         return sampling_sweep()
     if args.one_step:
-        return one_step(args.one_step, args.layers, args.batch, args.shape)
+        return one_step(args.one_step, args.layers, args.batch, args.shape, args.float32)
     if args.scenario:
         return scenario(args.scenario, args.shape, args.layers, args.generate)
     peaks = load_peaks()
