@@ -58,6 +58,48 @@ def test_norm_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    """The two parts around the layers, alone: rows of the table into the float32 residual stream (an
+    id beyond the table is flagged, not read), and float32 logits from the head's own matrix or,
+    tied, from the embedding's; a vocabulary and a width that are no power of two."""
+    from turboserve_b200.config import PartSpec
+    from turboserve_b200.engine.batch import RequestSlice
+    from turboserve_b200.parts import EMBEDDINGS, HEADS
+
+    hidden, vocab = 72, 101
+    embedding = EMBEDDINGS.get("table")(PartSpec("table"), hidden, vocab, dtype, DEV)
+    table = bind_random(embedding, dtype, seed=3)["weight"]
+    ids = [5, 100, 0, 17, 17, 64]
+    ctx = make_ctx([RequestSlice(ids, 0, [[0]])], 1, dtype)
+    residual = torch.full((6, hidden), float("nan"), device=DEV)
+    embedding.forward(residual, ctx)
+    assert torch.equal(residual.double().cpu(), table[torch.tensor(ids)]) and int(ctx.status.item()) == 0
+    assert embedding.table.dtype == dtype and embedding.scratch_per_token() == 0 and embedding.graph_safe
+    ctx.batch.token_ids[1] = vocab  # beyond the table
+    embedding.forward(residual, ctx)
+    assert int(ctx.status.item()) & 1
+
+    rows = torch.randn(4, hidden).to(dtype)
+    for tied in (False, True):
+        head = HEADS.get("linear")(PartSpec("linear"), hidden, vocab, dtype, DEV, tied=tied)
+        assert [p.name for p in head.param_specs()] == ([] if tied else ["weight"])
+        if tied:
+            head.bind({})
+            head.tie(embedding.table)
+            matrix = table
+            with pytest.raises(ValueError):
+                head.tie(embedding.table[:, :8])
+        else:
+            matrix = bind_random(head, dtype, seed=4)["weight"]
+        logits = torch.full((4, vocab), float("nan"), device=DEV)
+        head.forward(rows.to(DEV), logits, 3, ctx)
+        assert logits.dtype == torch.float32 and torch.isnan(logits[3]).all()  # only the rows that were asked for
+        ref = rows.double()[:3] @ matrix.T
+        bound = (2e-5 if dtype == torch.float32 else 2e-2) * max(1.0, ref.abs().max().item())
+        assert (logits[:3].double().cpu() - ref).abs().max().item() <= bound
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("act", ["silu", "gelu_pytorch_tanh"])
 def test_feed_forward_part(dtype, act):
     from turboserve_b200.config import PartSpec
