@@ -271,6 +271,55 @@ def test_random_arrivals_aborts_and_options_keep_every_sampled_id_right(model_fo
     assert counts["checked"] >= sum(len(v) for v in produced.values()) and counts["logprobs"] > 20
 
 
+def test_float32_tokens_do_not_depend_on_how_the_engine_is_configured(model_folders):
+    """Eighty requests with drawn lengths, arrival steps and options (filters, penalties, seeds) through three
+    float32 engines: roomy with graphs and steps launched ahead; a pool and budgets so tight that
+    requests are sent back and prompts cut into many portions; no graphs and nothing launched
+    ahead, other page and batch sizes. Float32 logits do not depend on the cut or the batch and a
+    draw depends on (seed, index) alone, so every request must get the very same tokens from all three."""
+    import random
+
+    from turboserve_b200 import EngineConfig, LLMEngine, SamplingParams, SchedulerConfig
+
+    config, _ = P.read_model_folder(model_folders["D"])
+    rng = random.Random(5)
+    requests = []
+    for i in range(80):
+        options = dict(max_tokens=rng.randint(1, 40), ignore_eos=True, temperature=rng.choice([0.0, 0.0, 0.8, 1.3]), seed=1000 + i)
+        if rng.random() < 0.4:
+            options.update(top_k=rng.choice([0, 3, 50]), top_p=rng.choice([1.0, 0.95, 0.5]))
+        if rng.random() < 0.4:
+            options["repetition_penalty"] = rng.choice([1.05, 1.3, 2.0])
+        requests.append((rng.randint(0, 120), f"r{i}", prompts_for(config, [rng.randint(1, 300)], seed=i)[0], SamplingParams(**options)))
+
+    def run(scheduler, **engine_options):
+        engine = LLMEngine(EngineConfig(model=str(model_folders["D"]), dtype="float32", seed=1,
+                                        scheduler=SchedulerConfig(**scheduler), **engine_options))
+        tokens = {}
+        with engine:
+            step = 0
+            while step <= 120 or engine.has_unfinished():
+                for when, rid, prompt, sampling in requests:
+                    if when == step:
+                        engine.add_request(rid, prompt, sampling)
+                for out in engine.step():
+                    tokens.setdefault(out.request_id, []).extend(out.new_token_ids)
+                step += 1
+                assert step < 20000
+            stats = engine.stats()
+            engine.scheduler.check_invariants()
+            assert engine.cache.free_pages() == [g.num_pages for g in engine.cache.groups]
+        return tokens, stats
+
+    roomy, stats_roomy = run(dict(max_num_seqs=16, max_num_batched_tokens=1024, block_size=16, num_blocks=1000))
+    tight, stats_tight = run(dict(max_num_seqs=5, max_num_batched_tokens=64, block_size=8, num_blocks=60))
+    plain, _ = run(dict(max_num_seqs=9, max_num_batched_tokens=333, block_size=32, num_blocks=150), cuda_graphs=False, overlap_decode=False)
+    assert stats_roomy["num_overlapped_steps"] > 0 and stats_tight["num_preemptions"] > 0
+    for _, rid, _, sampling in requests:
+        assert len(roomy[rid]) == sampling.max_tokens, rid
+        assert roomy[rid] == tight[rid] == plain[rid], rid
+
+
 def test_long_decoding_through_many_pages_and_a_window(model_folders):
     from turboserve_b200 import SamplingParams
 
