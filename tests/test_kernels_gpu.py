@@ -877,7 +877,7 @@ def test_sampling_with_options_by_state_slot_equals_sampling_with_options_by_row
     for slot, (t, k, p, s, plen) in slot_opts.items():
         temperature[slot], top_k[slot], top_p[slot], seed[slot], prompt_len[slot] = t, k, p, s, plen
     work = torch.empty(rows * vocab, device=DEV)
-    partial = torch.zeros(rows * (2 * chunks + 1), dtype=torch.int32, device=DEV)
+    partial = torch.zeros(rows * (4 * chunks + 1), dtype=torch.int32, device=DEV)
     dev = lambda t: t.to(DEV)
     for _ in range(2):  # twice: the counters in `partial` are left at zero
         tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
@@ -962,7 +962,7 @@ def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(v
     assert sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in marked[4]) == len(set(histories[0][1:]))
 
     work = torch.empty(rows * vocab, device=DEV)
-    partial = torch.zeros(rows * (2 * chunks + 1), dtype=torch.int32, device=DEV)
+    partial = torch.zeros(rows * (4 * chunks + 1), dtype=torch.int32, device=DEV)
     tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
     logprobs = torch.full((rows,), 123.0, device=DEV)
     kernels.sample_slots(logits, work, tokens, rows, temperature=dev(temperature), top_k=dev(top_k), top_p=dev(top_p),
@@ -994,8 +994,7 @@ def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(v
         assert tokens[r].item() == expect, r
         if o[4]:
             assert abs(logprobs[r].item() - logprob) < 1e-4
-            filtered = o[0] > 0 and (0 < o[1] < vocab or o[2] < 1.0)  # worked by a cluster: the row's sum in another order
-            assert abs(logprobs[r].item() - by_row_logprobs[r].item()) <= (1e-5 if filtered else 0.0)
+            assert abs(logprobs[r].item() - by_row_logprobs[r].item()) <= 1e-5  # the row's sum is added up in another order
         else:
             assert logprobs[r].item() == 123.0  # nobody asked: not written
     assert tokens[0].item() != logits[0].argmax().item()  # the penalty decided the greedy row

@@ -21,9 +21,11 @@
 // chunks), when all it needs is one pass: a greedy row, or a draw with neither top-k nor top-p
 // (no penalty, no log-probability either).  Every part finds its own best (value, id), leaves
 // it in `partial`, and the part that finishes last (an atomic count per row, no waiting) picks
-// among them; "larger value, lower id on ties" does not depend on the order.  A row that needs
-// the filters is worked by its first block alone.  `partial` holds rows * (2 * chunks + 1) words
-// and its counters must be zero before the first call; the kernel leaves them zero.
+// among them; "larger value, lower id on ties" does not depend on the order.  A row that wants
+// its log-probability also leaves each part's maximum and sum of exponentials, which the last
+// part adds up in the order of the parts.  A row that needs the filters is worked by its first
+// block alone.  `partial` holds rows * (4 * chunks + 1) words and its counters must be zero
+// before the first call; the kernel leaves them zero.
 //
 // Options may also be looked up by state slot (RowLookup, filled from a step's own index arrays):
 // row -> the step's token whose logits it holds (row_token, or the row itself) -> that token's
@@ -219,7 +221,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
 
   // -- one pass is enough: greedy, or a draw without filters ----------------------------------
   const int chunks = gridDim.y;
-  const bool one_pass = (pen == 1.0f || seen_row != nullptr) && !need_lse && (temp == 0.0f || (!(k > 0 && k < vocab) && !(p_option < 1.0f)));
+  const bool one_pass = (pen == 1.0f || seen_row != nullptr) && (temp == 0.0f || (!(k > 0 && k < vocab) && !(p_option < 1.0f)));
   if (one_pass && partial != nullptr) {
     const int per = (vocab + chunks - 1) / chunks;
     const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
@@ -235,21 +237,44 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
       }
     }
     pick = block_argmax(pick, arg_scratch);
+    // for a log-probability: this part's maximum and its sum of exponentials of the penalised logits
+    float part_max = -INFINITY, part_sum = 0.0f;
+    if (need_lse) {
+      for (int i = lo + tid; i < hi; i += blockDim.x) part_max = fmaxf(part_max, penalised(x[i], i, pen, seen_row));
+      part_max = block_max(part_max, f_scratch);
+      for (int i = lo + tid; i < hi; i += blockDim.x) part_sum += expf(penalised(x[i], i, pen, seen_row) - part_max);
+      part_sum = block_sum(part_sum, f_scratch);
+    }
     if (chunks == 1) {
-      if (tid == 0) tokens[row] = pick.index;
+      if (tid == 0) {
+        tokens[row] = pick.index;
+        if (need_lse) logprobs[row] = penalised(x[pick.index], pick.index, pen, seen_row) - (part_max + logf(part_sum));
+      }
       return;
     }
-    int* mine = partial + (size_t)row * (2 * chunks + 1);
+    // per row: a counter, then (value, id) of every part, then (maximum, sum) of every part
+    int* mine = partial + (size_t)row * (4 * chunks + 1);
     if (tid == 0) {
       mine[1 + 2 * blockIdx.y] = __float_as_int(pick.value);
       mine[2 + 2 * blockIdx.y] = pick.index;
+      if (need_lse) {
+        mine[1 + 2 * chunks + 2 * blockIdx.y] = __float_as_int(part_max);
+        mine[2 + 2 * chunks + 2 * blockIdx.y] = __float_as_int(part_sum);
+      }
       __threadfence();
-      if (atomicAdd(&mine[0], 1) == chunks - 1) {  // every other part has left its best behind
+      if (atomicAdd(&mine[0], 1) == chunks - 1) {  // every other part has left its results behind
         __threadfence();
         ArgMax all{-INFINITY, 0x7fffffff};
         for (int c = 0; c < chunks; ++c)
           all = better(all, ArgMax{__int_as_float(__ldcg(&mine[1 + 2 * c])), __ldcg(&mine[2 + 2 * c])});
         tokens[row] = all.index;
+        if (need_lse) {  // the parts' sums brought to the row's maximum, added in the order of the parts
+          float row_max = -INFINITY, row_sum = 0.0f;
+          for (int c = 0; c < chunks; ++c) row_max = fmaxf(row_max, __int_as_float(__ldcg(&mine[1 + 2 * chunks + 2 * c])));
+          for (int c = 0; c < chunks; ++c)
+            row_sum += __int_as_float(__ldcg(&mine[2 + 2 * chunks + 2 * c])) * expf(__int_as_float(__ldcg(&mine[1 + 2 * chunks + 2 * c])) - row_max);
+          logprobs[row] = penalised(x[all.index], all.index, pen, seen_row) - (row_max + logf(row_sum));
+        }
         mine[0] = 0;
       }
     }
@@ -715,7 +740,7 @@ TS_EXPORT int ts_sample(const float* logits, long long logits_stride, float* wor
 
 // Words of `partial` that ts_sample_slots needs for (rows, chunks).
 TS_EXPORT long long ts_sample_partial_words(int num_rows, int chunks) {
-  return (long long)num_rows * (2 * (long long)chunks + 1);
+  return (long long)num_rows * (4 * (long long)chunks + 1);
 }
 
 // The same with the options looked up by state slot (see the head of this file): temperature,
@@ -724,8 +749,7 @@ TS_EXPORT long long ts_sample_partial_words(int num_rows, int chunks) {
 // step's index arrays (RowLookup); `partial` is zeroed scratch of
 // ts_sample_partial_words(num_rows, chunks) words that the kernel leaves zeroed where it
 // matters, chunks >= 1.  A penalty other than 1 needs `seen` (seen_words words per slot).  A row
-// whose slot wants a log-probability gets it in logprobs[row] (worked by one block if it needs
-// no filter).
+// whose slot wants a log-probability gets it in logprobs[row].
 TS_EXPORT int ts_sample_slots(const float* logits, long long logits_stride, float* work, int num_rows,
                               int vocab, const float* temperature, const int* top_k, const float* top_p,
                               const unsigned long long* seed, const int* prompt_len, const int* row_token,

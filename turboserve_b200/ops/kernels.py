@@ -285,7 +285,7 @@ def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
     request in the step, negative for padding, whose row is skipped; without it the token itself),
     ``seq_slot`` and ``seq_context`` (per request: its state slot and its length after the step).
     The index of the token being generated is ``seq_context - prompt_len[slot]``. ``partial`` is
-    zeroed int32 scratch of ``rows * (2 * chunks + 1)`` words; a row that needs one pass only
+    zeroed int32 scratch of ``rows * (4 * chunks + 1)`` words; a row that needs one pass only
     (greedy, or a draw without top-k and top-p) is cut into ``chunks`` blocks.
 
     ``penalty`` (per slot) goes with ``seen`` (int32 ``[slots, ceil(vocab / 32)]``: the bitmap of the
@@ -308,7 +308,7 @@ def sample_slots(logits: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
                                 ("logprobs", logprobs, torch.float32)):
         if tensor is not None:
             _need(tensor, dtype, name)
-    if partial.numel() < num_rows * (2 * chunks + 1):
+    if partial.numel() < num_rows * (4 * chunks + 1):
         raise KernelError("sample_slots: partial is too small")
     if row_token is not None and row_token.numel() < num_rows:
         raise KernelError("sample_slots: row_token has fewer entries than rows")

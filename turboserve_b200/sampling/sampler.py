@@ -129,7 +129,7 @@ class Sampler:
         of :meth:`sample_by_slot` once, so that it can be part of a captured graph."""
         if self.slots is None or self.slots.num_slots < num_slots or self.slots.vocab != vocab:
             self.slots = SlotOptions(num_slots, vocab, self.device)
-            self._partial = torch.zeros(num_slots * (2 * SLOT_CHUNKS + 1), dtype=torch.int32, device=self.device)
+            self._partial = torch.zeros(num_slots * (4 * SLOT_CHUNKS + 1), dtype=torch.int32, device=self.device)
         self._scratch(num_slots, vocab)
         return self.slots
 
