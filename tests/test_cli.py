@@ -77,3 +77,13 @@ def test_generate_prints_tokens(model_folders):
     assert len(outputs) == 2 and all(len(json.loads(line.split(": ", 1)[1])) == 6 for line in outputs)
     assert result.stdout.count("6 tokens, finish_reason=length") == 2
     assert '"num_finished": 2' in result.stdout  # --stats
+
+
+@pytest.mark.gpu
+def test_generate_with_a_penalty_and_log_probabilities(model_folders):
+    result = runner.invoke(app, ["engine", "generate", "-m", str(model_folders["D"]), "--prompt-ids", "5,17,3,5,17,3", "--max-tokens", "8",
+                                 "--ignore-eos", "--num-blocks", "32", "--repetition-penalty", "1.5", "--logprobs"])
+    assert result.exit_code == 0, result.stdout
+    line = next(line for line in result.stdout.splitlines() if line.strip().startswith("logprobs:"))
+    values = [float(v) for v in line.split(":", 1)[1].split()]
+    assert len(values) == 8 and all(v <= 0.0 for v in values)

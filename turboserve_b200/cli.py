@@ -4,7 +4,9 @@
 with their meanings (``src/turboserve/engine/runtime/engine.py:522-606``; root app and
 ``version`` / ``hwinfo`` from ``src/turboserve/cli.py:43-95``). Options of subsystems this
 engine does not have (``--prefix-caching``, ``--offline``, ``--device cpu``) are absent.
-Added: prompts as token ids (``--prompt-ids``), ``engine random-weights`` (writes a model
+Added: prompts as token ids (``--prompt-ids``), ``--top-k``, ``--repetition-penalty`` and
+``--logprobs`` (fields of the reference's ``SamplingParams`` that its command line does not
+reach), ``engine random-weights`` (writes a model
 folder from a configuration and a seed) and ``engine replay`` (the trace-replay program).
 """
 
@@ -58,6 +60,8 @@ def generate_command(
     temperature: Annotated[float, typer.Option("--temperature", min=0.0)] = 0.0,
     top_p: Annotated[float, typer.Option("--top-p", min=0.0, max=1.0)] = 1.0,
     top_k: Annotated[int, typer.Option("--top-k", min=0)] = 0,
+    repetition_penalty: Annotated[float, typer.Option("--repetition-penalty", min=0.01, help="Above 1 makes tokens the request already holds less likely.")] = 1.0,
+    logprobs: Annotated[bool, typer.Option("--logprobs/--no-logprobs", help="Print the log-probability of every generated token.")] = False,
     seed: Annotated[Optional[int], typer.Option("--seed", help="Seed for stochastic sampling.")] = None,
     dtype: Annotated[str, typer.Option("--dtype", help="auto, bfloat16 or float32.")] = "auto",
     num_blocks: Annotated[Optional[int], typer.Option("--num-blocks", min=1, help="Skip memory profiling.")] = None,
@@ -86,7 +90,7 @@ def generate_command(
                                   block_size=block_size, num_blocks=num_blocks),
     )
     sampling = SamplingParams(max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k, seed=seed,
-                              ignore_eos=ignore_eos)
+                              ignore_eos=ignore_eos, repetition_penalty=repetition_penalty, logprobs=logprobs)
     with LLMEngine(config, tokenizer=tokenizer) as engine:
         started = time.perf_counter()
         outputs = engine.generate(prompts, sampling)
@@ -95,6 +99,8 @@ def generate_command(
             typer.echo(f"prompt {index}: {prompts[index]}")
             typer.echo(f"output {index}: {output.text_delta or output.token_ids}")
             typer.echo(f"  {output.output_tokens} tokens, finish_reason={output.finish_reason}")
+            if logprobs and output.logprobs is not None:
+                typer.echo("  logprobs: " + " ".join(f"{value:.4f}" for value in output.logprobs))
         typer.echo(f"{len(outputs)} completions in {elapsed:.2f}s")
         if show_stats:
             typer.echo(json.dumps(engine.stats(), indent=2, default=str))
