@@ -36,8 +36,10 @@ class KVCacheSizing:
 
 def activation_headroom_bytes(scratch_per_token: int, vocab: int, scheduler: SchedulerConfig) -> int:
     """Scratch the step needs at its largest batch: what the model's parts declare per token
-    (``DecoderModel.scratch_bytes_per_token``), and fp32 logits for every request, twice."""
-    return scheduler.max_num_batched_tokens * scratch_per_token + 2 * scheduler.max_num_seqs * vocab * 4
+    (``DecoderModel.scratch_bytes_per_token``), fp32 logits for every request, twice (the sampler's
+    scratch is as large), and the sampler's bit per vocabulary entry and request."""
+    seen_bits = scheduler.max_num_seqs * ((vocab + 31) // 32) * 4
+    return scheduler.max_num_batched_tokens * scratch_per_token + 2 * scheduler.max_num_seqs * vocab * 4 + seen_bits
 
 
 def device_memory_info(device: torch.device | None = None) -> tuple[int, int]:
