@@ -24,7 +24,7 @@ def test_pages_are_what_is_left_after_weights_and_scratch():
     sizing = size_kv_cache(model.cache_plan(), scheduler, 2, scratch_per_token=scratch, vocab=model.vocab_size,
                            gpu_memory_utilization=0.5, memory_info=(total - used, total))
     headroom = activation_headroom_bytes(scratch, model.vocab_size, scheduler)
-    assert headroom == 64 * scratch + 2 * 4 * 1000 * 4
+    assert headroom == 64 * scratch + 2 * 4 * 1000 * 4 + 4 * 32 * 4  # logits twice, a bit per request and vocabulary entry
     per_page = sum(model.cache_plan().bytes_per_page(8, 2))
     assert sizing.bytes_per_block == per_page and sizing.source == "memory"
     assert sizing.num_blocks == (total // 2 - used - headroom) // per_page
