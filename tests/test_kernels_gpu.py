@@ -379,8 +379,7 @@ def test_flash_decode_with_splits(nh, nkv, d, page, window, splits, tma):
     out = torch.full((n, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
     scratch = torch.full((max(4, fa.decode_scratch_floats(n, nh, splits, d)),), float("nan"), device=DEV)
     if tma:
-        if not fa.tma_decode_supports(d, page, nh // nkv):
-            pytest.skip("the TMA-fed kernel takes head size 128")
+        assert fa.tma_decode_supports(d, page, nh // nkv)
         status = torch.zeros(1, dtype=torch.int32, device=DEV)
         fa.flash_decode_tma(qp, out, k_pages, v_pages, table, pad(seq_of, -1), pad(positions, 0), n, nh, nkv, d, window, scale,
                             splits, scratch, status)
@@ -808,7 +807,7 @@ def test_decode_attention_that_encodes_and_appends_itself_equals_the_two_kernel_
     assert torch.equal(k_c, k_pages) and torch.equal(v_c, v_pages) and torch.equal(out_c[:live], out_b[:live])
 
 
-@pytest.mark.parametrize("kind", ["registers", "registers64", "tma", "fused"])
+@pytest.mark.parametrize("kind", ["registers", "registers64", "tma", "tma64", "fused"])
 def test_decode_kernels_mask_and_flag_a_page_that_is_missing_inside_the_visible_keys(kind):
     """A table entry of -1 inside a request's visible keys (a page given back too early) is never
     read as if it held zeros: its keys get no weight, and bit 4 of the status word says so.
@@ -816,7 +815,7 @@ def test_decode_kernels_mask_and_flag_a_page_that_is_missing_inside_the_visible_
     from turboserve_b200.ops import attention_bf16 as fa
 
     nh, nkv, page = 4, 2, 16
-    d = 64 if kind == "registers64" else 128
+    d = 64 if kind.endswith("64") else 128
     ctx, lost = 200, 5  # page 5 holds keys 80 .. 95
     k_dense, v_dense, k_pages, v_pages, table = paged_layout([ctx], page, nkv, d, torch.bfloat16, DEV, seed=51)
     q, positions, seq_of = pack_queries([ctx], [1], nh, d, torch.bfloat16, DEV, seed=52)
@@ -833,7 +832,7 @@ def test_decode_kernels_mask_and_flag_a_page_that_is_missing_inside_the_visible_
         scratch = torch.empty(max(4, fa.decode_scratch_floats(1, nh, 3, d)), device=DEV)
         if kind.startswith("registers"):
             fa.flash_decode(q, out, k_pages, v_pages, tab, seq_of, positions, 1, nh, nkv, d, window, scale, 3, scratch, status)
-        elif kind == "tma":
+        elif kind.startswith("tma"):
             fa.flash_decode_tma(q, out, k_pages, v_pages, tab, seq_of, positions, 1, nh, nkv, d, window, scale, 3, scratch, status)
         else:
             # the fused kernel takes the product: no bias, no rotation, and the token's own key and value in place
@@ -1000,15 +999,15 @@ def test_sampling_by_slot_with_a_penalty_from_the_bitmap_and_log_probabilities(v
     assert tokens[0].item() != logits[0].argmax().item()  # the penalty decided the greedy row
 
 
-@pytest.mark.parametrize("nh, nkv, page, window", [(28, 4, 16, None), (5, 1, 8, 300), (16, 2, 64, None)])
-def test_decode_attention_over_a_work_list(nh, nkv, page, window):
+@pytest.mark.parametrize("nh, nkv, d, page, window", [(28, 4, 128, 16, None), (5, 1, 128, 8, 300), (16, 2, 128, 64, None),
+                                                      (14, 2, 64, 16, None), (6, 2, 64, 4, 200)])
+def test_decode_attention_over_a_work_list(nh, nkv, d, page, window):
     """Every request cut into parts by its own length: more parts than a short request has 64-key tiles
     (some are empty), one part (the output is written at once, the join kernel skips it), unused
     items and a padding token at the end of the list."""
     from turboserve_b200.engine.batch import DecodeItems, plan_decode_items
     from turboserve_b200.ops import attention_bf16 as fa
 
-    d = 128
     contexts = [5000, 1, 70, 640, 129, 64]
     q_lens = [1] * len(contexts)
     _, q, k_pages, v_pages, table, positions, seq_of, ref, scale = flash_case(nh, nkv, d, page, window, contexts, q_lens, seed=61)

@@ -707,9 +707,8 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 #define DTMA_KEYS 64
 #define DTMA_STAGES 3
 #define DTMA_HALF 8192          // [64 keys x 64 dims] bf16
-#define DTMA_STAGE_BYTES 32768  // keys (two dim halves), then values (two dim halves)
 #define DTMA_THREADS (FLASH_THREADS + 32)
-#define DTMA_SMEM (DTMA_STAGES * DTMA_STAGE_BYTES + 1024)
+#define DTMA_SMEM(D) (DTMA_STAGES * 2 * ((D) / 64) * DTMA_HALF + 1024)
 #define DTMA_WAIT_LIMIT (1 << 24)
 
 __device__ __forceinline__ void dtma_mbar_init(unsigned bar, unsigned count) {
@@ -787,7 +786,7 @@ __device__ __forceinline__ void dtma_rotate(float x1, float x2, float c, float s
   o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
 }
 
-template <bool CLUSTER, bool FUSED>
+template <int D, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DTMA_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
@@ -797,7 +796,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         int window, float scale_log2, int num_splits, float* __restrict__ partial_o,
                         float* __restrict__ partial_ml, int* __restrict__ status, const DecodeFusion fusion,
                         const DecodeItems items) {
-  constexpr int D = 128;
+  static_assert(D == 64 || D == 128, "head size 64 or 128");
+  static_assert(!FUSED || D == 128, "the kernel encodes and appends itself for head size 128 only");
+  constexpr int HALVES = D / 64;                           // 64-dim halves of a key or value row
+  constexpr int STAGE_BYTES = 2 * HALVES * DTMA_HALF;      // keys (their halves), then values (theirs)
   constexpr int SLOTS = FUSED ? FLASH_WARPS + 1 : FLASH_WARPS;
   if (!FUSED) pdl_wait();  // no early trigger: with it the decode step was 0.2 ms slower (3.42 against 3.21 ms)
   extern __shared__ unsigned char dtma_raw[];
@@ -903,15 +905,15 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       if (lane == 0) {
         if (gone_boxes && status) atomicOr(status, 4);
         gone_s[st] = gone_boxes;  // before the arrival below, which releases it to the consumers
-        dtma_expect_tx(full0 + 8 * st, DTMA_STAGE_BYTES);
+        dtma_expect_tx(full0 + 8 * st, STAGE_BYTES);
       }
       __syncwarp();
       if (lane < boxes) {
-        const unsigned dst = ring + st * DTMA_STAGE_BYTES + lane * box_rows * 128;
+        const unsigned dst = ring + st * STAGE_BYTES + lane * box_rows * 128;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < HALVES; ++h) {
           dtma_load_2d(dst + h * DTMA_HALF, &map_k, kv_head * D + h * 64, row, full0 + 8 * st);
-          dtma_load_2d(dst + (2 + h) * DTMA_HALF, &map_v, kv_head * D + h * 64, row, full0 + 8 * st);
+          dtma_load_2d(dst + (HALVES + h) * DTMA_HALF, &map_v, kv_head * D + h * 64, row, full0 + 8 * st);
         }
       }
     }
@@ -1042,7 +1044,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         break;
       }
-      const unsigned keys = ring + st * DTMA_STAGE_BYTES, values = keys + 2 * DTMA_HALF;
+      const unsigned keys = ring + st * STAGE_BYTES, values = keys + HALVES * DTMA_HALF;
       float sc[2][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i)
@@ -1313,8 +1315,41 @@ static int dtma_make_map(CUtensorMap* map, const void* pages, long long rows, lo
   return res == CUDA_SUCCESS ? 0 : TS_ERR_ARGUMENT;
 }
 
-// Decode steps with head size 128 and pages of 4 to 2^30 tokens (a power of two), keys and values
-// fetched by TMA.  Splits and scratch as for ts_flash_decode; num_pages is the pool's size.
+// The launches of a checked call, for one head size.
+template <int D, bool FUSED>
+static int flash_decode_tma_launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, long long q_stride,
+                                   void* out, long long out_stride, const int* block_table, int table_stride,
+                                   const int* seq_of_token, const int* positions, int num_tokens, int shift, int box_rows,
+                                   long long rows, int num_heads, int num_kv_heads, int window, float scale_log2,
+                                   int num_splits, float* partial_o, float* partial_ml, int* status,
+                                   const DecodeFusion& fusion, bool cluster, const DecodeItems& items, int num_items,
+                                   cudaStream_t stream) {
+  const bool listed = items.item_token != nullptr;
+  const dim3 grid = listed ? dim3(num_items, num_kv_heads, 1) : dim3(num_splits, num_kv_heads, num_tokens);
+  if (cluster) {
+    cudaFuncSetAttribute(flash_decode_tma_kernel<D, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM(D));
+    ts_launch_cluster(flash_decode_tma_kernel<D, true, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM(D), stream, num_splits,
+                      map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride,
+                      seq_of_token, positions, shift, box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2,
+                      num_splits, (float*)nullptr, (float*)nullptr, status, fusion, items);
+    return ts_launch_status();
+  }
+  cudaFuncSetAttribute(flash_decode_tma_kernel<D, false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM(D));
+  ts_launch(flash_decode_tma_kernel<D, false, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM(D), stream, map_k, map_v,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token, positions, shift,
+            box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
+            fusion, items);
+  const int code = ts_launch_status();
+  if (code || (num_splits == 1 && !listed)) return code;
+  ts_launch(flash_decode_join_kernel<D>, dim3(num_heads, num_tokens), dim3(D), 0, stream, (bf16*)out, out_stride,
+            seq_of_token, num_heads, num_splits, (const float*)partial_o, (const float*)partial_ml, items.parts_of,
+            items.first_item);
+  return ts_launch_status();
+}
+
+// Decode steps with head size 64 or 128 (the form that encodes and appends itself: 128 only) and
+// pages of 4 to 2^30 tokens (a power of two), keys and values fetched by TMA.  Splits and
+// scratch as for ts_flash_decode; num_pages is the pool's size.
 template <bool FUSED>
 static int flash_decode_tma_checked(const void* q, long long q_stride, void* out, long long out_stride,
                                     const void* k_pages, const void* v_pages, long long num_pages,
@@ -1326,7 +1361,7 @@ static int flash_decode_tma_checked(const void* q, long long q_stride, void* out
   if (num_tokens <= 0) return 0;
   const int bad = check_common(q, q_stride, out, out_stride, head_dim, num_heads, num_kv_heads, page_size);
   if (bad) return bad;
-  if (head_dim != 128 || page_size < 4) return TS_ERR_SIZE;
+  if ((head_dim != 128 && (FUSED || head_dim != 64)) || page_size < 4) return TS_ERR_SIZE;
   if (num_heads / num_kv_heads > 16) return TS_ERR_SIZE;
   if (((uintptr_t)q & 3) || (q_stride & 1)) return TS_ERR_ALIGN;
   if (((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return TS_ERR_ALIGN;
@@ -1350,26 +1385,17 @@ static int flash_decode_tma_checked(const void* q, long long q_stride, void* out
   // scratch: the partial rows of every slot, then their (max, sum): [tokens, heads, splits], or [items, heads]
   const size_t slots = listed ? (size_t)num_items * num_heads : (size_t)num_tokens * num_heads * num_splits;
   float* partial_ml = scratch ? scratch + slots * head_dim : nullptr;
-  const dim3 grid = listed ? dim3(num_items, num_kv_heads, 1) : dim3(num_splits, num_kv_heads, num_tokens);
-  if (cluster) {
-    cudaFuncSetAttribute(flash_decode_tma_kernel<true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
-    ts_launch_cluster(flash_decode_tma_kernel<true, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, num_splits, map_k,
-                      map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token,
-                      positions, shift, box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits,
-                      (float*)nullptr, (float*)nullptr, status, fusion, items);
-    return ts_launch_status();
-  }
-  cudaFuncSetAttribute(flash_decode_tma_kernel<false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DTMA_SMEM);
-  ts_launch(flash_decode_tma_kernel<false, FUSED>, grid, dim3(DTMA_THREADS), DTMA_SMEM, stream, map_k, map_v,
-            (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, seq_of_token, positions, shift,
-            box_rows, (int)rows, num_heads, num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
-            fusion, items);
-  code = ts_launch_status();
-  if (code || (num_splits == 1 && !listed)) return code;
-  ts_launch(flash_decode_join_kernel<128>, dim3(num_heads, num_tokens), dim3(128), 0, stream, (bf16*)out, out_stride,
-            seq_of_token, num_heads, num_splits, (const float*)partial_o, (const float*)partial_ml, items.parts_of,
-            items.first_item);
-  return ts_launch_status();
+  if (head_dim == 128)
+    return flash_decode_tma_launch<128, FUSED>(map_k, map_v, q, q_stride, out, out_stride, block_table, table_stride,
+                                               seq_of_token, positions, num_tokens, shift, box_rows, rows, num_heads,
+                                               num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
+                                               fusion, cluster, items, num_items, stream);
+  if constexpr (!FUSED)
+    return flash_decode_tma_launch<64, false>(map_k, map_v, q, q_stride, out, out_stride, block_table, table_stride,
+                                              seq_of_token, positions, num_tokens, shift, box_rows, rows, num_heads,
+                                              num_kv_heads, window, scale_log2, num_splits, partial_o, partial_ml, status,
+                                              fusion, cluster, items, num_items, stream);
+  return TS_ERR_SIZE;
 }
 
 TS_EXPORT int ts_flash_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,

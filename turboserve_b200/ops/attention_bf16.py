@@ -4,8 +4,8 @@ Rules (explicit; what they refuse goes to the generic kernel, see ``ops/attentio
 head size 64 or 128, page size a power of two, at most 64 query heads per kv head. A step with
 prompts in it and head size 128 runs the TMA + tcgen05 kernel of ``attention_tc.cu`` when that
 takes the shape (``attention_tc.supports``), else the tiled ``mma.sync`` kernel here. A decode
-step (at most 16 query heads per kv head) with head size 128 and pages of at least 4 tokens
-runs the TMA-fed decode kernel, else the register-fed one; it is cut along the keys into
+step (at most 16 query heads per kv head) with pages of at least 4 tokens runs the TMA-fed
+decode kernel, else the register-fed one; it is cut along the keys into
 ``num_splits`` parts, a function of the number of tokens, kv heads and SMs only, so the same
 launch shape serves a captured graph at any context length.
 """
@@ -24,7 +24,7 @@ from .skinny import num_sms
 
 MAX_SPLITS = 32
 TMA_DECODE = os.environ.get("TURBOSERVE_B200_DECODE_TMA", "1") != "0"
-"""Decode steps with head size 128 fetch keys and values by TMA (``flash_decode_tma``); 0 keeps the register-fed kernel."""
+"""Decode steps fetch keys and values by TMA (``flash_decode_tma``); 0 keeps the register-fed kernel."""
 CLUSTER_MAX_SPLITS = 8
 """Up to this many splits are the blocks of one thread-block cluster and are joined over
 distributed shared memory, with no scratch and no second kernel."""
@@ -104,13 +104,13 @@ def flash_decode(q, out, k_pages, v_pages, block_table, seq_of_token, positions,
 
 
 def tma_decode_supports(head_dim: int, page_size: int, group: int) -> bool:
-    """Head size 128, pages of at least 4 tokens (a power of two), at most 16 query heads per kv head."""
-    return head_dim == 128 and page_size >= 4 and page_size & (page_size - 1) == 0 and group <= 16
+    """Head size 64 or 128, pages of at least 4 tokens (a power of two), at most 16 query heads per kv head."""
+    return head_dim in (64, 128) and page_size >= 4 and page_size & (page_size - 1) == 0 and group <= 16
 
 
 def flash_decode_tma(q, out, k_pages, v_pages, block_table, seq_of_token, positions, num_tokens, num_heads, num_kv_heads,
                      head_dim, window, scale, num_splits, scratch, status=None) -> None:
-    """Attention for a decode step with keys and values fetched by TMA (head size 128); arguments as :func:`flash_decode`."""
+    """Attention for a decode step with keys and values fetched by TMA; arguments as :func:`flash_decode`."""
     _common(q, out, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim)
     _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
     if num_splits > CLUSTER_MAX_SPLITS:
@@ -193,7 +193,7 @@ def can_fuse_decode(qkv: torch.Tensor, k_pages: torch.Tensor, batch, num_heads: 
     """Whether this step's attention can take the raw q/k/v product (:func:`flash_decode_tma_fused`):
     a decode-only bfloat16 step whose shape the TMA-fed kernel takes, with the mixer's own keys and values."""
     return (FUSED_DECODE and TMA_DECODE and qkv.dtype == torch.bfloat16 and batch.is_decode_only and scale > 0
-            and tma_decode_supports(head_dim, k_pages.shape[1], num_heads // num_kv_heads)
+            and head_dim == 128 and tma_decode_supports(head_dim, k_pages.shape[1], num_heads // num_kv_heads)
             and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and qkv.shape[1] >= (num_heads + 2 * num_kv_heads) * head_dim
             and 0 <= rotary_dim <= head_dim and rotary_dim % 2 == 0)
 
