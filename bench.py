@@ -39,6 +39,9 @@ SHAPES = {
     "0.5b": ("Qwen2-0.5B", dict(QWEN2_7B, num_hidden_layers=24, hidden_size=896, num_attention_heads=14,
                                  num_key_value_heads=2, head_dim=64, intermediate_size=4864, vocab_size=151936,
                                  tie_word_embeddings=True)),
+    "1.5b": ("Qwen2-1.5B", dict(QWEN2_7B, num_hidden_layers=28, hidden_size=1536, num_attention_heads=12,
+                                 num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936,
+                                 tie_word_embeddings=True)),
     "7b": ("Qwen2-7B", QWEN2_7B),
     "14b": ("Qwen2.5-14B", dict(QWEN2_7B, num_hidden_layers=48, hidden_size=5120, num_attention_heads=40,
                                 num_key_value_heads=8, intermediate_size=13824, rms_norm_eps=1e-5)),
